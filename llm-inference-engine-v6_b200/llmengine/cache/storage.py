@@ -53,7 +53,8 @@ def bytes_per_token(run_needs: Sequence[Sequence[object]], dtype: torch.dtype) -
     for needs in run_needs:
         for n in needs:
             if isinstance(n, KVNeed):
-                total += 2 * n.num_kv_heads * n.head_dim * el
+                vd = n.head_dim if n.value_dim is None else n.value_dim
+                total += n.num_kv_heads * (n.head_dim + vd) * el
     return total
 
 
@@ -68,7 +69,9 @@ def allocate_run_caches(run_needs: Sequence[Sequence[object]], run_group: Sequen
                 shape = (group_pages[g] + 1, n.num_kv_heads, page_size, n.head_dim)
                 c.group, c.window = g, windows[g]
                 c.k = torch.zeros(shape, dtype=dtype, device=device)
-                c.v = torch.zeros(shape, dtype=dtype, device=device)
+                vd = n.head_dim if n.value_dim is None else n.value_dim
+                if vd > 0:  # 0: the values are a part of the key rows, no tensor of their own
+                    c.v = torch.zeros(shape[:3] + (vd,), dtype=dtype, device=device)
             elif isinstance(n, StateNeed):
                 c.states[n.name] = torch.zeros((num_slots + 1,) + tuple(n.shape), dtype=n.dtype, device=device)
             else:

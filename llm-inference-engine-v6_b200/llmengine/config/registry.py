@@ -45,8 +45,12 @@ def get_architecture(name: str) -> Architecture:
 
 
 def architecture_name_of(config_json: Dict[str, Any]) -> str:
+    """The name a configuration goes by: the first of `architectures`, or the string `architecture`."""
     archs = config_json.get("architectures")
     if not archs:
+        one = config_json.get("architecture")
+        if isinstance(one, str) and one:
+            return one
         raise ConfigError("config.json: missing key 'architectures'")
     if not isinstance(archs, list) or not isinstance(archs[0], str):
         raise ConfigError("config.json: 'architectures' must be a list of names")

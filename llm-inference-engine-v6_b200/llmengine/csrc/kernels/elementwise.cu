@@ -254,8 +254,14 @@ __device__ __forceinline__ void gate_up_columns(int c, int ff, int block, size_t
   }
 }
 
+// act 0: silu, g / (1 + exp(-g)); act 1: the tanh form of gelu, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))
+__device__ __forceinline__ float gate_activation(float g, int act) {
+  if (act == 1) return 0.5f * g * (1.0f + tanhf(0.79788456080286535588f * (g + 0.044715f * g * g * g)));
+  return g / (1.0f + expf(-g));
+}
+
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int ff, size_t total, int block) {
+__global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int ff, size_t total, int block, int act) {
   dep_launch();
   dep_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -266,20 +272,21 @@ __global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, i
   gate_up_columns(c, ff, block, &gc, &uc);
   const float g = to_f32(in[r * 2 * ff + gc]);
   const float u = to_f32(in[r * 2 * ff + uc]);
-  float s = g / (1.0f + expf(-g));
+  float s = gate_activation(g, act);
   out[i] = from_f32<T>(s * u);
 }
 
-extern "C" int llm_silu_mul(const void* in, void* out, int dtype, int n_rows, int ff, int block, cudaStream_t stream) {
+extern "C" int llm_silu_mul(const void* in, void* out, int dtype, int n_rows, int ff, int block, int act, cudaStream_t stream) {
   if (n_rows == 0) return LLM_OK;
   LLM_REQUIRE(n_rows > 0 && ff > 0, "silu_mul: bad sizes rows=%d ff=%d", n_rows, ff);
   LLM_REQUIRE(block >= 0 && (block == 0 || ff % block == 0), "silu_mul: column block %d does not divide %d", block, ff);
+  LLM_REQUIRE(act == 0 || act == 1, "silu_mul: unknown activation %d", act);
   const size_t total = (size_t)n_rows * ff;
   const int blocks = ceil_div((long long)total, 256);
   if (dtype == LLM_F32)
-    launch_kernel(silu_mul_kernel<float>, blocks, 256, 0, stream, (const float*)in, (float*)out, ff, total, block);
+    launch_kernel(silu_mul_kernel<float>, blocks, 256, 0, stream, (const float*)in, (float*)out, ff, total, block, act);
   else if (dtype == LLM_BF16)
-    launch_kernel(silu_mul_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)in, (bf16*)out, ff, total, block);
+    launch_kernel(silu_mul_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)in, (bf16*)out, ff, total, block, act);
   else
     LLM_REQUIRE(false, "silu_mul: unknown dtype %d", dtype);
   LLM_CHECK_LAUNCH("silu_mul");
@@ -319,7 +326,7 @@ extern "C" int llm_reduce_partials(const float* partials, int n_partials, long l
 // partials: [parts, rows, 2*ff] float32 (gate | up); out [rows, ff] = silu(sum gate) * (sum up).
 template <typename T>
 __global__ void silu_mul_partials_kernel(const float* __restrict__ partials, int n_partials, size_t stride,
-                                         T* __restrict__ out, int ff, size_t total, int block, const RowScale rs) {
+                                         T* __restrict__ out, int ff, size_t total, int block, const RowScale rs, int act) {
   dep_launch();
   dep_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -347,13 +354,13 @@ __global__ void silu_mul_partials_kernel(const float* __restrict__ partials, int
   const float sc = row_scale(rs, r);  // the norm before the product, when its 1/rms is still owed
   g *= sc;
   u *= sc;
-  const float s = g / (1.0f + expf(-g));
+  const float s = gate_activation(g, act);
   out[i] = from_f32<T>(s * u);
 }
 
 extern "C" int llm_silu_mul_partials(const float* partials, int n_partials, long long stride, void* out, int out_dtype,
                                      int n_rows, int ff, int block, const float* sumsq, int n_sumsq, float inv_dim, float eps,
-                                     cudaStream_t stream) {
+                                     int act, cudaStream_t stream) {
   if (n_rows == 0) return LLM_OK;
   const RowScale rs{sumsq, n_sumsq, inv_dim, eps};
   LLM_REQUIRE(n_rows > 0 && ff > 0 && n_partials >= 1, "silu_mul_partials: bad sizes");
@@ -361,11 +368,83 @@ extern "C" int llm_silu_mul_partials(const float* partials, int n_partials, long
   const size_t total = (size_t)n_rows * ff;
   const int blocks = ceil_div((long long)total, 256);
   if (out_dtype == LLM_F32)
-    launch_kernel(silu_mul_partials_kernel<float>, blocks, 256, 0, stream, partials, n_partials, (size_t)stride, (float*)out, ff, total, block, rs);
+    launch_kernel(silu_mul_partials_kernel<float>, blocks, 256, 0, stream, partials, n_partials, (size_t)stride, (float*)out, ff, total, block, rs, act);
   else if (out_dtype == LLM_BF16)
-    launch_kernel(silu_mul_partials_kernel<bf16>, blocks, 256, 0, stream, partials, n_partials, (size_t)stride, (bf16*)out, ff, total, block, rs);
+    launch_kernel(silu_mul_partials_kernel<bf16>, blocks, 256, 0, stream, partials, n_partials, (size_t)stride, (bf16*)out, ff, total, block, rs, act);
   else
     LLM_REQUIRE(false, "silu_mul_partials: unknown dtype %d", out_dtype);
   LLM_CHECK_LAUNCH("silu_mul_partials");
+  return LLM_OK;
+}
+
+// ------------------------------------------------------------------------------------ token side input
+// out[t, j] = gelu_tanh(z[t, j]) * table[ids[t], col0 + j]: a gate computed from the stream times the
+// token's own row of a second embedding table (columns col0 .. col0 + dim).
+template <typename T>
+__global__ void token_gate_kernel(const T* __restrict__ z, const T* __restrict__ table, long long ld_table, int col0,
+                                  const int* __restrict__ ids, int vocab, T* __restrict__ out, int dim, size_t total) {
+  dep_launch();
+  dep_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t t = i / dim;
+  const int j = (int)(i - t * dim);
+  int id = ids[t];
+  if (id < 0 || id >= vocab) id = 0;
+  out[i] = from_f32<T>(gate_activation(to_f32(z[i]), 1) * to_f32(table[(size_t)id * ld_table + col0 + j]));
+}
+
+extern "C" int llm_token_gate(const void* z, const void* table, long long ld_table, int col0, const int* ids, int vocab, void* out,
+                              int n_rows, int dim, int dtype, cudaStream_t stream) {
+  if (n_rows == 0) return LLM_OK;
+  LLM_REQUIRE(n_rows > 0 && dim > 0 && col0 >= 0 && col0 + dim <= ld_table && vocab > 0, "token_gate: bad sizes");
+  const size_t total = (size_t)n_rows * dim;
+  const int blocks = ceil_div((long long)total, 256);
+  if (dtype == LLM_F32)
+    launch_kernel(token_gate_kernel<float>, blocks, 256, 0, stream, (const float*)z, (const float*)table, ld_table, col0, ids, vocab, (float*)out, dim, total);
+  else if (dtype == LLM_BF16)
+    launch_kernel(token_gate_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)z, (const bf16*)table, ld_table, col0, ids, vocab, (bf16*)out, dim, total);
+  else
+    LLM_REQUIRE(false, "token_gate: unknown dtype %d", dtype);
+  LLM_CHECK_LAUNCH("token_gate");
+  return LLM_OK;
+}
+
+// h += a (+ b), each float32 [parts, rows, dim] partial sums added in index order, a before b; then
+// copy (may be null) = h in the engine's dtype: the stream as the operand of a product.
+template <typename T>
+__global__ void stream_add_kernel(float* __restrict__ h, const float* __restrict__ a, int na, size_t sa, const float* __restrict__ b,
+                                  int nb, size_t sb, T* __restrict__ copy, size_t total) {
+  dep_launch();
+  dep_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  float x = h[i];
+  if (a) {
+    float d = a[i];
+    for (int p = 1; p < na; ++p) d += a[(size_t)p * sa + i];
+    x += d;
+  }
+  if (b) {
+    float d = b[i];
+    for (int p = 1; p < nb; ++p) d += b[(size_t)p * sb + i];
+    x += d;
+  }
+  h[i] = x;
+  if (copy) copy[i] = from_f32<T>(x);
+}
+
+extern "C" int llm_stream_add(float* h, const float* a, int na, long long sa, const float* b, int nb, long long sb, void* copy,
+                              int copy_dtype, long long total, cudaStream_t stream) {
+  if (total == 0) return LLM_OK;
+  LLM_REQUIRE(total > 0 && (a == nullptr || na >= 1) && (b == nullptr || nb >= 1), "stream_add: bad sizes");
+  const int blocks = ceil_div(total, 256);
+  if (copy_dtype == LLM_F32)
+    launch_kernel(stream_add_kernel<float>, blocks, 256, 0, stream, h, a, na, (size_t)sa, b, nb, (size_t)sb, (float*)copy, (size_t)total);
+  else if (copy_dtype == LLM_BF16)
+    launch_kernel(stream_add_kernel<bf16>, blocks, 256, 0, stream, h, a, na, (size_t)sa, b, nb, (size_t)sb, (bf16*)copy, (size_t)total);
+  else
+    LLM_REQUIRE(false, "stream_add: unknown dtype %d", copy_dtype);
+  LLM_CHECK_LAUNCH("stream_add");
   return LLM_OK;
 }

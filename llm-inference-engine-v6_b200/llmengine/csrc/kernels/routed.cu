@@ -1,0 +1,218 @@
+// Routed feed-forward (mixture of experts) on CUDA cores: router, grouping of the step's (token, choice)
+// pairs by expert, per-expert products, and the weighted sum. Everything has fixed shapes given the
+// number of tokens, so a step can be recorded as a CUDA graph.
+//
+//   route     z = Wr x + b in float32; the `top` largest logits (the lower index wins a tie); their weights
+//             are the softmax over the chosen logits only
+//   group     pairs (token * top + choice) sorted by expert into tiles of `tile` rows; a tile holds rows of
+//             one expert (the last tile of an expert is padded with -1); tile_expert[i] = -1 for unused tiles
+//   product   for every tile: rows of a (picked by pair / a_div) times the expert's matrix; the result row
+//             is written at the pair's index, so no inverse permutation is needed. Epilogue: the exact
+//             (erf) gelu, or the pair's weight
+//   combine   out[t] = sum over the token's choices, in index order
+#include "common.cuh"
+
+#include <cfloat>
+#include <cmath>
+
+namespace {
+
+template <typename T>
+__global__ void route_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ wr, const float* __restrict__ bias,
+                             int D, int E, int top, int* __restrict__ idx, float* __restrict__ share) {
+  extern __shared__ float z[];  // E
+  dep_launch();
+  dep_wait();
+  const int tok = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const T* xr = x + (size_t)tok * ldx;
+  for (int e = warp; e < E; e += nw) {
+    const T* w = wr + (size_t)e * D;
+    float acc = 0.f;
+    for (int k = lane; k < D; k += 32) acc = fmaf(to_f32(xr[k]), to_f32(w[k]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) z[e] = acc + (bias ? bias[e] : 0.f);
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  // warp 0 picks the largest `top` times; lanes scan strided, ties go to the lower index
+  float zmax = 0.f, denom = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = z[e];
+      if (v > best) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (k == 0) zmax = best;
+    const float p = expf(best - zmax);
+    denom += p;
+    if (lane == 0) {
+      idx[(size_t)tok * top + k] = bi;
+      share[(size_t)tok * top + k] = p;
+      z[bi] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  if (lane < top) share[(size_t)tok * top + lane] /= denom;
+}
+
+// One block. counts -> tiles per expert -> scatter. The order of an expert's rows depends on timing;
+// every row's result is computed on its own, so nothing depends on that order.
+__global__ void group_kernel(const int* __restrict__ idx, int n_pairs, int E, int tile, int max_tiles, int* __restrict__ tile_expert,
+                             int* __restrict__ tile_rows) {
+  extern __shared__ int sh[];  // counts[E], start[E] (in rows, tile-aligned), cursor[E]
+  int* counts = sh;
+  int* start = sh + E;
+  int* cursor = sh + 2 * E;
+  dep_launch();
+  dep_wait();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = cursor[e] = 0;
+  for (int i = threadIdx.x; i < max_tiles; i += blockDim.x) tile_expert[i] = -1;
+  for (int i = threadIdx.x; i < max_tiles * tile; i += blockDim.x) tile_rows[i] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&counts[idx[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < E; ++e) {
+      start[e] = at * tile;
+      const int nt = (counts[e] + tile - 1) / tile;
+      for (int k = 0; k < nt; ++k) tile_expert[at + k] = e;
+      at += nt;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int e = idx[i];
+    tile_rows[start[e] + atomicAdd(&cursor[e], 1)] = i;
+  }
+}
+
+constexpr int RP_WARPS = 4, RP_ROWS = 8;  // rows of a tile of the CUDA-core product
+
+// epilogue 0: exact gelu; 1: times share[pair]
+template <typename TA, typename TO>
+__global__ void __launch_bounds__(RP_WARPS * 32)
+    routed_product_kernel(const TA* __restrict__ a, long long lda, int a_div, const TA* __restrict__ w, long long w_stride, int N, int K,
+                          const int* __restrict__ tile_expert, const int* __restrict__ tile_rows, TO* __restrict__ out, long long ldo,
+                          int epilogue, const float* __restrict__ share) {
+  dep_launch();
+  dep_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int e = tile_expert[blockIdx.y];
+  const int n = blockIdx.x * RP_WARPS + warp;
+  if (e < 0 || n >= N) return;
+  const int* rows = tile_rows + (size_t)blockIdx.y * RP_ROWS;
+  int pair[RP_ROWS];
+  const TA* ar[RP_ROWS];
+#pragma unroll
+  for (int i = 0; i < RP_ROWS; ++i) {
+    pair[i] = rows[i];
+    ar[i] = pair[i] >= 0 ? a + (size_t)(pair[i] / a_div) * lda : nullptr;
+  }
+  const TA* wrow = w + (size_t)e * w_stride + (size_t)n * K;
+  float acc[RP_ROWS];
+#pragma unroll
+  for (int i = 0; i < RP_ROWS; ++i) acc[i] = 0.f;
+  for (int k = lane; k < K; k += 32) {
+    const float wv = to_f32(wrow[k]);
+#pragma unroll
+    for (int i = 0; i < RP_ROWS; ++i)
+      if (ar[i]) acc[i] = fmaf(to_f32(ar[i][k]), wv, acc[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < RP_ROWS; ++i) acc[i] = warp_sum(acc[i]);
+  if (lane < RP_ROWS) {
+    float v = 0.f;
+    int p = -1;
+#pragma unroll
+    for (int i = 0; i < RP_ROWS; ++i)
+      if (i == lane) { v = acc[i]; p = pair[i]; }
+    if (p >= 0) {
+      if (epilogue == 0) v = 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
+      else v *= share[p];
+      out[(size_t)p * ldo + n] = from_f32<TO>(v);
+    }
+  }
+}
+
+__global__ void combine_kernel(const float* __restrict__ y, float* __restrict__ out, int top, int D, size_t total) {
+  dep_launch();
+  dep_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t t = i / D;
+  const int c = (int)(i - t * D);
+  float s = 0.f;
+  for (int k = 0; k < top; ++k) s += y[(t * top + k) * D + c];
+  out[i] = s;
+}
+
+}  // namespace
+
+extern "C" int llm_route(const void* x, long long ldx, const void* wr, const float* bias, int n_tokens, int D, int E, int top,
+                         int* idx, float* share, int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(n_tokens > 0 && D > 0 && E > 0 && top > 0 && top <= E, "route: bad sizes experts=%d top=%d", E, top);
+  LLM_REQUIRE(top <= 32 && E <= 8192, "route: at most 32 of 8192 experts a token (got %d of %d)", top, E);
+  const size_t smem = (size_t)E * sizeof(float);
+  if (dtype == LLM_F32)
+    launch_kernel(route_kernel<float>, n_tokens, 128, smem, stream, (const float*)x, ldx, (const float*)wr, bias, D, E, top, idx, share);
+  else if (dtype == LLM_BF16)
+    launch_kernel(route_kernel<bf16>, n_tokens, 128, smem, stream, (const bf16*)x, ldx, (const bf16*)wr, bias, D, E, top, idx, share);
+  else
+    LLM_REQUIRE(false, "route: unknown dtype %d", dtype);
+  LLM_CHECK_LAUNCH("route");
+  return LLM_OK;
+}
+
+extern "C" int llm_routed_tiles(int n_pairs, int E, int tile) { return (n_pairs + tile - 1) / tile + E; }
+
+extern "C" int llm_routed_group(const int* idx, int n_pairs, int E, int tile, int max_tiles, int* tile_expert, int* tile_rows,
+                                cudaStream_t stream) {
+  if (n_pairs == 0) return LLM_OK;
+  LLM_REQUIRE(n_pairs > 0 && E > 0 && tile > 0 && E <= 4096, "routed_group: bad sizes");
+  LLM_REQUIRE(max_tiles >= llm_routed_tiles(n_pairs, E, tile), "routed_group: room for %d tiles, %d may be needed", max_tiles,
+              llm_routed_tiles(n_pairs, E, tile));
+  launch_kernel(group_kernel, 1, 1024, (size_t)3 * E * sizeof(int), stream, idx, n_pairs, E, tile, max_tiles, tile_expert, tile_rows);
+  LLM_CHECK_LAUNCH("routed_group");
+  return LLM_OK;
+}
+
+// a: rows picked by pair / a_div; w [E, N, K]; out rows at the pair's index. in_dtype: a and w; out_dtype: out.
+extern "C" int llm_routed_product(const void* a, long long lda, int a_div, const void* w, int N, int K, const int* tile_expert,
+                                  const int* tile_rows, int max_tiles, void* out, long long ldo, int epilogue, const float* share,
+                                  int in_dtype, int out_dtype, cudaStream_t stream) {
+  if (max_tiles == 0) return LLM_OK;
+  LLM_REQUIRE(N > 0 && K > 0 && a_div > 0 && max_tiles > 0 && max_tiles <= 65535, "routed_product: bad sizes");
+  LLM_REQUIRE(epilogue == 0 || (epilogue == 1 && share), "routed_product: unknown epilogue %d", epilogue);
+  dim3 grid(ceil_div(N, RP_WARPS), max_tiles);
+  const long long ws = (long long)N * K;
+#define LLM_RP(TA, TO)                                                                                                         \
+  launch_kernel(routed_product_kernel<TA, TO>, grid, RP_WARPS * 32, 0, stream, (const TA*)a, lda, a_div, (const TA*)w, ws, N, K, \
+                tile_expert, tile_rows, (TO*)out, ldo, epilogue, share)
+  if (in_dtype == LLM_F32 && out_dtype == LLM_F32) LLM_RP(float, float);
+  else if (in_dtype == LLM_BF16 && out_dtype == LLM_BF16) LLM_RP(bf16, bf16);
+  else if (in_dtype == LLM_BF16 && out_dtype == LLM_F32) LLM_RP(bf16, float);
+  else LLM_REQUIRE(false, "routed_product: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
+#undef LLM_RP
+  LLM_CHECK_LAUNCH("routed_product");
+  return LLM_OK;
+}
+
+extern "C" int llm_routed_product_rows() { return RP_ROWS; }
+
+extern "C" int llm_routed_combine(const float* y, float* out, int n_tokens, int top, int D, cudaStream_t stream) {
+  if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(n_tokens > 0 && top > 0 && D > 0, "routed_combine: bad sizes");
+  const size_t total = (size_t)n_tokens * D;
+  launch_kernel(combine_kernel, ceil_div((long long)total, 256), 256, 0, stream, y, out, top, D, total);
+  LLM_CHECK_LAUNCH("routed_combine");
+  return LLM_OK;
+}

@@ -115,7 +115,19 @@ class Model:
         res.sumsq, ctx.stream_sumsq = ctx.stream_sumsq, None
         if ctx.stream_prescaled is not None:
             (res.prescaled, res.prescaled_weight), ctx.stream_prescaled = ctx.stream_prescaled, None
+        x0 = None
+        if any(run.add_embedding for run in order):
+            # the layer order adds the embedding's output again later: the rows are looked up once more, now, into a
+            # buffer that no layer writes
+            x0 = self.embedding.lookup(ctx, ctx.ws.get("model.embedding_out", tuple(res.h.shape), torch.float32))
         for r, run in enumerate(order):
+            if run.add_embedding:
+                if res.pending is not None:
+                    self.env.ops.stream_add(res.h, res.pending, x0, n_rows=ctx.n_tokens)
+                    res.pending = None
+                else:
+                    res.pending = x0
+                res.sumsq = res.prescaled = res.prescaled_weight = None
             ctx.norm_after_block = self.blocks[order[r + 1].layer].first_norm() if r + 1 < len(order) else self.final_norm
             res = self.blocks[run.layer].forward(res, ctx, self.caches[r])
         ctx.next_norm = ctx.norm_after_block = None

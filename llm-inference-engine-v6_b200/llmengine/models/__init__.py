@@ -1,2 +1,2 @@
-"""Architectures: each module registers one name of config.json `architectures`."""
-from . import llama  # noqa: F401
+"""Architectures: each module registers one name of config.json `architectures` (or `architecture`)."""
+from . import llama, vapelix  # noqa: F401

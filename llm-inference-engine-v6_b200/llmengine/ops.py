@@ -212,19 +212,23 @@ class CudaOps:
                                          _stream()), lib)
         return h
 
-    def silu_mul(self, gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> torch.Tensor:
-        """gate_up [n, 2*ff] -> out [n, ff] = silu(gate)*up. block 0: gate columns first, then up;
+    ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}  # what a gated feed-forward may apply to its gate
+
+    def silu_mul(self, gate_up: torch.Tensor, out: torch.Tensor, block: int = 0, act: str = "silu") -> torch.Tensor:
+        """gate_up [n, 2*ff] -> out [n, ff] = act(gate)*up. block 0: gate columns first, then up;
         block b: blocks of 2b columns, b of gate followed by the b matching ones of up."""
         _need(gate_up, "silu_mul.in"); _need(out, "silu_mul.out", gate_up.dtype)
         lib = self.lib()
         n, ff = out.shape
         assert gate_up.is_contiguous() and out.is_contiguous() and gate_up.shape == (n, 2 * ff)
         self._check(lib.llm_silu_mul(_ptr(gate_up), _ptr(out), c_int(dtype_code(out.dtype)), c_int(n), c_int(ff),
-                                     c_int(block), _stream()), lib)
+                                     c_int(block), c_int(self.ACTIVATIONS[act]), _stream()), lib)
         return out
 
+    EPILOGUE_ACTIVATIONS = ("silu",)  # what the gate|up product applies in its own epilogue (gemm_swiglu)
+
     def gemm_swiglu(self, a: torch.Tensor, w_blocked: torch.Tensor, out: torch.Tensor, ws=None,
-                    row_scale: Optional[RowScale] = None) -> torch.Tensor:
+                    row_scale: Optional[RowScale] = None, act: str = "silu") -> torch.Tensor:
         """out [m, ff] = silu(gate) * up where gate | up = a @ w_blocked.T and w_blocked [2*ff, k] holds
         blocks of 128 gate rows followed by the 128 matching up rows. With many tokens in bfloat16
         the activation is applied in the product's epilogue and the [m, 2*ff] intermediate never
@@ -233,7 +237,7 @@ class CudaOps:
         m, k = a.shape
         ff = out.shape[1]
         assert w_blocked.shape == (2 * ff, k) and out.shape[0] == m and out.is_contiguous() and ff % 128 == 0
-        if m > self.SWAP_MAX_TOKENS and self._tc_usable(a, w_blocked):
+        if m > self.SWAP_MAX_TOKENS and act in self.EPILOGUE_ACTIVATIONS and self._tc_usable(a, w_blocked):
             assert row_scale is None, "a row scale is applied where partial sums are consumed (few tokens)"
             lib = self.lib("tensorcore")
             self._check(lib.llm_gemm_tc_swiglu(_ptr(a), _ptr(w_blocked), _ptr(out), c_int(m), c_int(ff), c_int(k),
@@ -242,11 +246,11 @@ class CudaOps:
             return out
         assert ws is not None, "gemm_swiglu needs a workspace when it cannot fuse"
         if m <= self.SWAP_MAX_TOKENS:
-            return self.silu_mul_partials(self.gemm_partials(a, w_blocked, ws, "swiglu.parts"), out, block=128, row_scale=row_scale)
+            return self.silu_mul_partials(self.gemm_partials(a, w_blocked, ws, "swiglu.parts"), out, block=128, row_scale=row_scale, act=act)
         assert row_scale is None, "a row scale is applied where partial sums are consumed (few tokens)"
         gate_up = ws.get("swiglu.gate_up", (m, 2 * ff), a.dtype)
         self.gemm(a, w_blocked, gate_up)
-        return self.silu_mul(gate_up, out, block=128)
+        return self.silu_mul(gate_up, out, block=128, act=act)
 
     # ------------------------------------------------------------------ matrix products
     # A weight-streaming product (few tokens) is bound by memory; measured on B200 it streams fastest
@@ -308,6 +312,21 @@ class CudaOps:
                                       c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
                                       c_int(dtype_code(a.dtype)), c_int(dtype_code(out.dtype)), _stream()), lib)
         return out
+
+    def gemm_heads(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+        """out[:, h, :] = a[:, h, :] @ w[h].T head by head on the tensor-core product (a [n, H, K], w [H, N, K], out
+        [n, H, N]; views whose last dimension is contiguous). False, with nothing done, when the operands are not
+        what that kernel takes (the caller then uses heads_product)."""
+        H = w.shape[0]
+        if a.dtype != torch.bfloat16 or not all(self._tc_usable(a[:, h], w[h]) for h in (0, H - 1)):
+            return False
+        if out.data_ptr() % 16 or (out.stride(1) * 2) % 16 or (out.stride(0) * 2) % 16:
+            return False
+        for h in range(H):
+            self._gemm_tc(a[:, h], w[h], out[:, h])
+            self.launches += 1
+        self.launches -= 1
+        return True
 
     def gemm_partials(self, a: torch.Tensor, w: torch.Tensor, ws, tag: str) -> torch.Tensor:
         """As gemm, for consumers that add partial sums themselves: returns float32 [parts, M, N]
@@ -486,7 +505,7 @@ class CudaOps:
         return out
 
     def silu_mul_partials(self, parts: torch.Tensor, out: torch.Tensor, block: int = 0,
-                          row_scale: Optional[RowScale] = None) -> torch.Tensor:
+                          row_scale: Optional[RowScale] = None, act: str = "silu") -> torch.Tensor:
         """parts float32 [p, n, 2*ff] (gate | up partial sums, columns laid out as in silu_mul)
         -> out [n, ff] = silu(gate) * up; with row_scale, gate and up of row n are first multiplied by it."""
         _need(parts, "silu_mul.parts", torch.float32); _need(out, "silu_mul.out")
@@ -495,7 +514,7 @@ class CudaOps:
         lib = self.lib()
         self._check(lib.llm_silu_mul_partials(_ptr(parts), c_int(parts.shape[0]), c_longlong(parts.stride(0)), _ptr(out),
                                               c_int(dtype_code(out.dtype)), c_int(n), c_int(ff), c_int(block),
-                                              *_row_scale_args(row_scale), _stream()), lib)
+                                              *_row_scale_args(row_scale), c_int(self.ACTIVATIONS[act]), _stream()), lib)
         return out
 
     def tensor_core_error(self) -> int:
@@ -732,6 +751,194 @@ class CudaOps:
         if not self.tensor_cores:
             prompt = decode = "CUDA cores"
         return prompt, decode
+
+    # ------------------------------------------------------------------ stream and token side input
+    def stream_add(self, h: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor] = None,
+                   copy: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> torch.Tensor:
+        """h[:n] += a (+ b): float32 [n, dim] or [parts, n, dim] partial sums added in index order, a before b;
+        copy[:n] (optional, float32 or bfloat16) = the new h, the stream as an operand of a product."""
+        _need(h, "stream_add.h", torch.float32)
+        n = h.shape[0] if n_rows is None else n_rows
+        lib = self.lib()
+        args = []
+        for t, name in ((a, "a"), (b, "b")):
+            if t is None:
+                args += [c_void_p(0), c_int(0), c_longlong(0)]
+                continue
+            _need(t, "stream_add." + name, torch.float32)
+            assert t.is_contiguous() and t.shape[-1] == h.shape[-1] and t.shape[-2] == h.shape[0]
+            args += [_ptr(t), c_int(t.shape[0] if t.dim() == 3 else 1), c_longlong(t.stride(0) if t.dim() == 3 else 0)]
+        code = F32
+        if copy is not None:
+            _need(copy, "stream_add.copy")
+            assert copy.is_contiguous() and copy.shape[-1] == h.shape[-1] and copy.shape[0] >= n
+            code = dtype_code(copy.dtype)
+        assert h.is_contiguous()
+        self._check(lib.llm_stream_add(_ptr(h), *args, _ptr(copy), c_int(code), c_longlong(n * h.shape[-1]), _stream()), lib)
+        return h
+
+    def token_gate(self, z: torch.Tensor, table: torch.Tensor, col0: int, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """out[t, j] = gelu_tanh(z[t, j]) * table[ids[t], col0 + j]; z, out [n, dim] contiguous, of the table's dtype."""
+        _need(z, "token_gate.z"); _need(table, "token_gate.table", z.dtype); _need(out, "token_gate.out", z.dtype)
+        _need(ids, "token_gate.ids", torch.int32)
+        n, dim = out.shape
+        assert z.is_contiguous() and out.is_contiguous() and z.shape == out.shape and ids.numel() >= n
+        lib = self.lib()
+        self._check(lib.llm_token_gate(_ptr(z), _ptr(table), c_longlong(table.stride(0)), c_int(col0), _ptr(ids), c_int(table.shape[0]),
+                                       _ptr(out), c_int(n), c_int(dim), c_int(dtype_code(z.dtype)), _stream()), lib)
+        return out
+
+    # ------------------------------------------------------------------ latent attention
+    def latent_prep(self, parts: torch.Tensor, q_off: int, q_rank: int, kv_off: int, kv_rank: int, rot_dim: int, rot_dims: int,
+                    wq: torch.Tensor, wkv: torch.Tensor, eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                    batch, block_table: torch.Tensor, cq: torch.Tensor, cache: Optional[torch.Tensor]) -> None:
+        """From the float32 partial sums parts [p, n, width] of the mixer's first product: cq [n, q_rank] = the RMS-normed
+        query latent (weight wq); the cache row [c | kr] of every token, c = the RMS-normed first kv_rank numbers of the
+        key/value columns (weight wkv), kr = the next rot_dim with the first rot_dims rotated by cos/sin [positions, rot_dims/2].
+        cache [pages, 1, page_size, kv_rank + rot_dim], or None for a run that writes none."""
+        _need(parts, "latent_prep.parts", torch.float32); _need(cq, "latent_prep.cq"); _need(block_table, "latent_prep.block_table", torch.int32)
+        _need(wq, "latent_prep.wq", torch.float32); _need(wkv, "latent_prep.wkv", torch.float32)
+        n = batch.n_tokens
+        assert parts.is_contiguous() and parts.dim() == 3 and parts.shape[1] >= n and block_table.is_contiguous()
+        assert wq.numel() == q_rank and wkv.numel() == kv_rank and cq.shape[0] >= n and cq.shape[1] == q_rank
+        page = 1
+        if cache is not None:
+            _need(cache, "latent_prep.cache", cq.dtype)
+            assert cache.is_contiguous() and cache.shape[1] == 1 and cache.shape[3] == kv_rank + rot_dim
+            page = cache.shape[2]
+        if rot_dims:
+            _need(cos, "latent_prep.cos", torch.float32); _need(sin, "latent_prep.sin", torch.float32)
+            assert cos.is_contiguous() and sin.is_contiguous() and cos.shape[1] == rot_dims // 2 and cos.shape == sin.shape
+        lib = self.lib()
+        self._check(lib.llm_latent_prep(_ptr(parts), c_int(parts.shape[0]), c_longlong(parts.stride(0)), c_int(parts.shape[2]),
+                                        c_int(q_off), c_int(q_rank), c_int(kv_off), c_int(kv_rank), c_int(rot_dim), c_int(rot_dims),
+                                        _ptr(wq), _ptr(wkv), c_float(eps), _ptr(cos), _ptr(sin), _ptr(batch.positions),
+                                        _ptr(batch.token_seq), _ptr(block_table), c_int(block_table.shape[1]), _ptr(cq),
+                                        c_longlong(cq.stride(0)), _ptr(cache), c_int(page), c_int(dtype_code(cq.dtype)), c_int(n),
+                                        _stream()), lib)
+
+    def heads_product(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None,
+                      gate_off: int = 0) -> torch.Tensor:
+        """out[t, h, :] = w[h] a[t, h, :] for a [n, H, K], w [H, N, K], out [n, H, N] (views whose last dimension is
+        contiguous); with gate (float32 partial sums [p, n, width]), times sigmoid(sum_p gate[p, t, gate_off + h*N + j])."""
+        _need(a, "heads_product.a"); _need(w, "heads_product.w", a.dtype); _need(out, "heads_product.out", a.dtype)
+        n, H, K = a.shape
+        N = w.shape[1]
+        assert w.shape == (H, N, K) and w.is_contiguous() and out.shape == (n, H, N)
+        gargs = (c_void_p(0), c_int(0), c_longlong(0), c_int(0), c_int(0))
+        if gate is not None:
+            _need(gate, "heads_product.gate", torch.float32)
+            assert gate.is_contiguous() and gate.dim() == 3 and gate.shape[1] >= n and gate_off + H * N <= gate.shape[2]
+            gargs = (_ptr(gate), c_int(gate.shape[0]), c_longlong(gate.stride(0)), c_int(gate.shape[2]), c_int(gate_off))
+        lib = self.lib()
+        self._check(lib.llm_heads_product(_ptr(a), c_longlong(a.stride(0)), c_longlong(a.stride(1)), _ptr(w), c_longlong(K), _ptr(out),
+                                          c_longlong(out.stride(0)), c_longlong(out.stride(1)), c_int(n), c_int(H), c_int(N), c_int(K),
+                                          *gargs, c_int(dtype_code(a.dtype)), _stream()), lib)
+        return out
+
+    def latent_query(self, q: torch.Tensor, wkt: Optional[torch.Tensor], ql: torch.Tensor, heads: int, dim: int, rot_dim: int,
+                     kv_rank: int, rot_dims: int, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], positions: torch.Tensor,
+                     absorb: bool = True) -> torch.Tensor:
+        """q [n, H*(dim+rot_dim)] -> ql [n, H, kv_rank+rot_dim]: per head, wkt[h] (the head's key map transposed,
+        [kv_rank, dim]) applied to the unrotated part, unless absorb is False (then the caller writes those columns),
+        followed by the rotated part, its first rot_dims numbers turned by the token's position."""
+        _need(q, "latent_query.q"); _need(ql, "latent_query.ql", q.dtype); _need(positions, "latent_query.positions", torch.int32)
+        n = ql.shape[0]
+        assert ql.is_contiguous() and ql.shape == (n, heads, kv_rank + rot_dim) and q.shape[1] == heads * (dim + rot_dim)
+        if absorb:
+            _need(wkt, "latent_query.wkt", q.dtype)
+            assert wkt.is_contiguous() and wkt.shape == (heads, kv_rank, dim)
+        lib = self.lib()
+        self._check(lib.llm_latent_query(_ptr(q), c_longlong(q.stride(0)), _ptr(wkt), _ptr(ql), c_int(n), c_int(heads), c_int(dim),
+                                         c_int(rot_dim), c_int(kv_rank), c_int(rot_dims), c_int(1 if absorb else 0), _ptr(cos), _ptr(sin),
+                                         _ptr(positions), c_int(dtype_code(q.dtype)), _stream()), lib)
+        return ql
+
+    def latent_attention(self, ql: torch.Tensor, cache: torch.Tensor, batch, block_table: torch.Tensor, out: torch.Tensor,
+                         kv_rank: int, scale: float, window: int = 0) -> torch.Tensor:
+        """Causal softmax attention of every token of the step over the cached rows lo..pos of its request: ql [n, H, Dk]
+        against cache [pages, 1, page_size, Dk]; the values are the first kv_rank numbers of the rows; out [n, H, kv_rank]."""
+        _need(ql, "latent_attention.ql"); _need(cache, "latent_attention.cache", ql.dtype); _need(out, "latent_attention.out", ql.dtype)
+        _need(block_table, "latent_attention.block_table", torch.int32)
+        n, H, Dk = ql.shape
+        assert ql.is_contiguous() and out.is_contiguous() and cache.is_contiguous() and block_table.is_contiguous()
+        assert cache.shape[1] == 1 and cache.shape[3] == Dk and out.shape == (n, H, kv_rank) and n >= batch.n_tokens
+        lib = self.lib()
+        self._check(lib.llm_latent_attention_simt(_ptr(ql), _ptr(cache), c_int(dtype_code(ql.dtype)), _ptr(batch.positions),
+                                                  _ptr(batch.token_seq), _ptr(block_table), c_int(block_table.shape[1]), _ptr(out),
+                                                  c_int(batch.n_tokens), c_int(H), c_int(kv_rank), c_int(Dk - kv_rank),
+                                                  c_int(cache.shape[2]), c_float(scale), c_int(window), _stream()), lib)
+        return out
+
+    def sigmoid_gate(self, x: torch.Tensor, gate: torch.Tensor, gate_off: int) -> torch.Tensor:
+        """x[t, j] *= sigmoid(sum_p gate[p, t, gate_off + j]); gate float32 partial sums [p, n, width]."""
+        _need(x, "sigmoid_gate.x"); _need(gate, "sigmoid_gate.gate", torch.float32)
+        n, cols = x.shape
+        assert gate.is_contiguous() and gate.dim() == 3 and gate.shape[1] >= n
+        lib = self.lib()
+        self._check(lib.llm_sigmoid_gate(_ptr(x), c_longlong(x.stride(0)), _ptr(gate), c_int(gate.shape[0]), c_longlong(gate.stride(0)),
+                                         c_int(gate.shape[2]), c_int(gate_off), c_int(n), c_int(cols), c_int(dtype_code(x.dtype)),
+                                         _stream()), lib)
+        return x
+
+    # ------------------------------------------------------------------ routed feed-forward
+    def route(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], top: int, idx: torch.Tensor,
+              share: torch.Tensor) -> None:
+        """Per token: logits = w x + bias in float32, idx [n, top] (int32) = the experts with the largest logits (the lower
+        index wins a tie), share [n, top] (float32) = the softmax over the chosen logits."""
+        _need(x, "route.x"); _need(w, "route.w", x.dtype); _need(idx, "route.idx", torch.int32); _need(share, "route.share", torch.float32)
+        n, D = x.shape
+        E = w.shape[0]
+        assert w.is_contiguous() and w.shape[1] == D and idx.is_contiguous() and share.is_contiguous()
+        assert idx.shape == (n, top) and share.shape == (n, top)
+        if bias is not None:
+            _need(bias, "route.bias", torch.float32)
+            assert bias.numel() == E
+        lib = self.lib()
+        self._check(lib.llm_route(_ptr(x), c_longlong(x.stride(0)), _ptr(w), _ptr(bias), c_int(n), c_int(D), c_int(E), c_int(top),
+                                  _ptr(idx), _ptr(share), c_int(dtype_code(x.dtype)), _stream()), lib)
+
+    def routed_tile_rows(self, n_tokens: int = 0, dtype: Optional[torch.dtype] = None) -> int:
+        """Rows of a tile of the per-expert products."""
+        return int(self.lib().llm_routed_product_rows())
+
+    def routed_group(self, idx: torch.Tensor, experts: int, tile: int, ws, tag: str):
+        """Sorts the step's (token, choice) pairs by expert into tiles of `tile` rows -> (tile_expert [tiles] with -1 for
+        unused tiles, tile_rows [tiles, tile] with -1 for padding); a pair is token * top + choice."""
+        _need(idx, "routed_group.idx", torch.int32)
+        lib = self.lib()
+        pairs = idx.numel()
+        tiles = int(lib.llm_routed_tiles(c_int(pairs), c_int(experts), c_int(tile)))
+        tile_expert = ws.get(tag + ".tile_expert", (tiles,), torch.int32)
+        tile_rows = ws.get(tag + ".tile_rows", (tiles, tile), torch.int32)
+        self._check(lib.llm_routed_group(_ptr(idx), c_int(pairs), c_int(experts), c_int(tile), c_int(tiles), _ptr(tile_expert),
+                                         _ptr(tile_rows), _stream()), lib)
+        return tile_expert, tile_rows
+
+    def routed_product(self, a: torch.Tensor, a_div: int, w: torch.Tensor, tile_expert: torch.Tensor, tile_rows: torch.Tensor,
+                       out: torch.Tensor, epilogue: str, share: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """For every pair p of every tile (expert e): out[p, :] = epi(w[e] a[p // a_div, :]); w [E, N, K]. epilogue "gelu":
+        the exact (erf) gelu; "share": times share[p] (float32, flat)."""
+        _need(a, "routed_product.a"); _need(w, "routed_product.w", a.dtype); _need(out, "routed_product.out")
+        E, N, K = w.shape
+        assert w.is_contiguous() and a.shape[1] == K and out.shape[1] == N and tile_rows.shape[1] == self.routed_tile_rows()
+        if epilogue == "share":
+            _need(share, "routed_product.share", torch.float32)
+        lib = self.lib()
+        self._check(lib.llm_routed_product(_ptr(a), c_longlong(a.stride(0)), c_int(a_div), _ptr(w), c_int(N), c_int(K), _ptr(tile_expert),
+                                           _ptr(tile_rows), c_int(tile_expert.numel()), _ptr(out), c_longlong(out.stride(0)),
+                                           c_int({"gelu": 0, "share": 1}[epilogue]), _ptr(share), c_int(dtype_code(a.dtype)),
+                                           c_int(dtype_code(out.dtype)), _stream()), lib)
+        return out
+
+    def routed_combine(self, y: torch.Tensor, out: torch.Tensor, top: int) -> torch.Tensor:
+        """out[t, :] = sum_k y[t * top + k, :] in index order; float32."""
+        _need(y, "routed_combine.y", torch.float32); _need(out, "routed_combine.out", torch.float32)
+        n, D = out.shape
+        assert y.is_contiguous() and out.is_contiguous() and y.shape == (n * top, D)
+        lib = self.lib()
+        self._check(lib.llm_routed_combine(_ptr(y), _ptr(out), c_int(n), c_int(top), c_int(D), _stream()), lib)
+        return out
 
     # ------------------------------------------------------------------ sampling
     def sample_scratch_words(self, n_rows: int, vocab: int) -> int:

@@ -26,11 +26,13 @@ class BuildEnv:
 @dataclass(frozen=True)
 class KVNeed:
     """Keys and values per token, kept in pages. window 0: all of them; W: the last W.
-    portion_multiple: see StateNeed."""
+    portion_multiple: see StateNeed. value_dim: size of a value row; None = head_dim; 0 = no value tensor
+    (a mixer whose values are a part of its key rows)."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
     portion_multiple: int = 1
+    value_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -148,6 +150,11 @@ class Embedding(Part):
         (see Residual.sumsq)."""
         raise NotImplementedError
 
+    def lookup(self, ctx, out: torch.Tensor) -> torch.Tensor:
+        """The same rows once more into `out` (float32 [tokens, hidden]), for a model whose layer order adds the
+        embedding's output to the stream again (LayerRun.add_embedding)."""
+        raise NotImplementedError
+
 
 class Head(Part):
     category = "head"
@@ -172,6 +179,10 @@ class Norm(Part):
         """Adds res.pending into res.h (when `rows` is None) and returns the normalised rows in the
         engine dtype. With `rows`, only those source rows are normalised and res is left alone.
         Norms with can_defer take `lazy=True` as well (asked for only when the consumer wants it)."""
+        raise NotImplementedError
+
+    def run(self, h: torch.Tensor, ctx, rows, n: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The norm of rows of a float32 stream h that has nothing pending, h left as it is; into `out` if given."""
         raise NotImplementedError
 
 
@@ -216,6 +227,15 @@ class FeedForward(Part):
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         """As Mixer.forward, without a cache."""
+        raise NotImplementedError
+
+
+class TokenInput(Part):
+    category = "token_input"
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        """x: the residual stream [tokens, hidden] in the engine dtype (as an operand). Returns the float32 delta
+        [tokens, hidden] to be added to the stream; it reads the step's tokens from ctx.token_ids."""
         raise NotImplementedError
 
 

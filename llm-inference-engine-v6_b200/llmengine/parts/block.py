@@ -1,5 +1,7 @@
 """Arrangement of parts in a layer. "pre_norm": h += mixer(norm1(h)); h += feed_forward(norm2(h))
-(src/engine.cpp:307-413). The residual sums are fused into the norm that follows them."""
+(src/engine.cpp:307-413). The residual sums are fused into the norm that follows them.
+"parallel": h += mixer(norm1(h)) + feed_forward(norm2(h)), both norms of the same h; then an optional
+input from the tokens themselves, h += token_input(h)."""
 from __future__ import annotations
 
 from typing import List
@@ -56,4 +58,72 @@ class PreNormBlock(Block):
         return norm.forward(res, ctx)
 
 
+class ParallelBlock(Block):
+    """Mixer and feed-forward read the same stream through a norm each; their results are added together.
+    What is pending on the stream is added by the first norm; the two deltas are added by one kernel, which
+    also leaves the stream in the engine dtype when a token input wants it as an operand; the token input's
+    delta is left pending for the next reader."""
+
+    def __init__(self, spec: BlockSpec, env):
+        super().__init__(spec, env)
+        self.norm1 = build_part("norm", spec.norm1, env)
+        self.mixer = build_part("mixer", spec.mixer, env)
+        self.feed_forward = self.norm2 = self.token_input = None
+        if spec.feed_forward is not None:
+            self.norm2 = build_part("norm", spec.norm2, env)
+            self.feed_forward = build_part("feed_forward", spec.feed_forward, env)
+        if spec.token_input is not None:
+            self.token_input = build_part("token_input", spec.token_input, env)
+
+    @staticmethod
+    def tensor_needs(spec: BlockSpec) -> List[TensorNeed]:
+        out: List[TensorNeed] = []
+        subs = [("norm", spec.norm1), ("mixer", spec.mixer)]
+        if spec.feed_forward is not None:
+            subs += [("norm", spec.norm2), ("feed_forward", spec.feed_forward)]
+        if spec.token_input is not None:
+            subs.append(("token_input", spec.token_input))
+        for cat, sub in subs:
+            out += part_class(cat, sub.kind).tensor_needs(sub)
+        return out
+
+    def subparts(self):
+        return tuple(p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward, self.token_input) if p is not None)
+
+    def cache_needs(self):
+        return self.mixer.cache_needs()
+
+    def load(self, tensors) -> None:
+        for p in self.subparts():
+            p.load(tensors)
+
+    def first_norm(self):
+        return self.norm1
+
+    def forward(self, res: Residual, ctx, cache: LayerCache) -> Residual:
+        ops, n = self.env.ops, ctx.n_tokens
+        ctx.residual = ctx.next_norm = None  # the parts' last products return their sums; nobody adds into the stream
+        x1 = self.norm1.forward(res, ctx)    # adds what is pending
+        # the second norm's rows go to a buffer of their own: the mixer runs first and both read the same stream
+        x2 = None
+        if self.feed_forward is not None:
+            x2 = ctx.ws.get("block.norm2_out", (n, res.h.shape[1]), self.env.dtype)
+            self.norm2.run(res.h, ctx, None, n, out=x2)
+        a = self.mixer.forward(x1, ctx, cache)
+        b = self.feed_forward.forward(x2, ctx) if self.feed_forward is not None else None
+        if self.token_input is None:
+            if b is None:
+                res.pending = a
+            else:
+                ops.stream_add(res.h, a, b, n_rows=n)
+            res.sumsq = res.prescaled = res.prescaled_weight = None
+            return res
+        xs = ctx.ws.get("block.stream_copy", (n, res.h.shape[1]), self.env.dtype)
+        ops.stream_add(res.h, a, b, copy=xs, n_rows=n)
+        res.sumsq = res.prescaled = res.prescaled_weight = None
+        res.pending = self.token_input.forward(xs, ctx)
+        return res
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "parallel", ParallelBlock)

@@ -51,6 +51,10 @@ class TokenLookup(Embedding):
         return ops.embed(self.table, ctx.token_ids, h)
 
 
+    def lookup(self, ctx, out: torch.Tensor) -> torch.Tensor:
+        return self.env.ops.embed(self.table, ctx.token_ids, out)
+
+
 class LinearHead(Head):
     def __init__(self, spec: HeadSpec, env):
         super().__init__(spec, env)

@@ -18,8 +18,8 @@ from .spec import GatedMLPSpec, TensorNeed
 class GatedMLP(FeedForward):
     def __init__(self, spec: GatedMLPSpec, env):
         super().__init__(spec, env)
-        if spec.activation != "silu":
-            raise ValueError(f"gated feed-forward: activation '{spec.activation}' is not implemented (silu is)")
+        if spec.activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"gated feed-forward: activation '{spec.activation}' is not implemented (silu and gelu_tanh are)")
         self.w_gate_up = None
         self.w_down = None
 
@@ -43,7 +43,9 @@ class GatedMLP(FeedForward):
     def load(self, tensors) -> None:
         s = self.spec
         g, u = tensors[s.gate_weight], tensors[s.up_weight]
-        self.blocked = g.dtype == torch.bfloat16 and s.intermediate % 128 == 0
+        ops = self.env.ops
+        fused = s.activation == "silu" or s.activation in getattr(ops, "EPILOGUE_ACTIVATIONS", ())
+        self.blocked = g.dtype == torch.bfloat16 and s.intermediate % 128 == 0 and fused
         if self.blocked:
             self.w_gate_up = torch.stack([g.view(-1, 128, s.hidden), u.view(-1, 128, s.hidden)], dim=1).reshape(2 * s.intermediate, s.hidden).contiguous()
         else:
@@ -52,7 +54,7 @@ class GatedMLP(FeedForward):
 
     def _few_tokens(self, ctx) -> bool:
         s, ops, n = self.spec, self.env.ops, ctx.n_tokens
-        return (self.blocked and hasattr(ops, "gemm_few_tokens") and
+        return (self.blocked and s.activation == "silu" and hasattr(ops, "gemm_few_tokens") and
                 ops.few_token_splits(2 * s.intermediate, s.hidden, n, "swiglu") > 0 and
                 ops.few_token_splits(s.hidden, s.intermediate, n, "residual") > 0)
 
@@ -82,6 +84,8 @@ class GatedMLP(FeedForward):
                 extra, x = {"row_scale": x.row_scale(ops)}, x.prescaled
             else:
                 x = x.dense(ctx)
+        if s.activation != "silu":
+            extra["act"] = s.activation
         if self.blocked:
             ops.gemm_swiglu(x[:n], self.w_gate_up, act, ctx.ws, **extra)
         elif n <= 64:  # few tokens: the products may come as partial sums, added by their consumers
@@ -89,7 +93,7 @@ class GatedMLP(FeedForward):
         else:
             gate_up = ctx.ws.get("mlp.gate_up", (n, 2 * s.intermediate), self.env.dtype)
             ops.gemm(x[:n], self.w_gate_up, gate_up)
-            ops.silu_mul(gate_up, act)
+            ops.silu_mul(gate_up, act, **({"act": s.activation} if s.activation != "silu" else {}))
         return add_into_stream_or_partials(ops, act, self.w_down, ctx, False, "mlp.delta")
 
 

@@ -43,9 +43,11 @@ class RMSNorm(Norm):
     def prescale_weight(self):
         return self.weight
 
-    def run(self, h: torch.Tensor, ctx, rows, n: int) -> torch.Tensor:
-        """The norm's kernel on rows of a stream that has nothing pending (NormalizedRows.dense)."""
-        out = ctx.ws.get("norm.out" if rows is None else "norm.rows_out", (n, self.spec.dim), self.env.dtype)
+    def run(self, h: torch.Tensor, ctx, rows, n: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The norm's kernel on rows of a stream that has nothing pending (NormalizedRows.dense); into `out` if
+        given (a block whose two norms read the same stream keeps their rows apart)."""
+        if out is None:
+            out = ctx.ws.get("norm.out" if rows is None else "norm.rows_out", (n, self.spec.dim), self.env.dtype)
         self.env.ops.rmsnorm(h, self.weight, self.spec.eps, out, rows=rows, n_rows=n)
         return out
 

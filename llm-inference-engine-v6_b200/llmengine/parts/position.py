@@ -17,7 +17,7 @@ import torch
 
 from .base import LayerCache, PositionEncoding
 from .registry import register_part
-from .spec import PositionSpec
+from .spec import PositionSpec, ScaledRotarySpec
 
 _PI_F32 = float(np.float32(3.14159265358979323846))
 
@@ -88,6 +88,53 @@ class RotaryPosition(PositionEncoding):
                                    num_kv_heads, head_dim, parts=parts, **extra)
 
 
+def ramp_frequencies(spec: ScaledRotarySpec):
+    """-> (float64 frequencies of the dims/2 pairs, the factor on cos and sin) of a ScaledRotarySpec."""
+    dims, base = int(spec.dims), float(spec.base)
+    f = np.asarray([base ** (-2.0 * i / dims) for i in range(dims // 2)], dtype=np.float64)
+    if spec.factor <= 0:
+        return f, 1.0
+
+    def turn(t: float) -> float:
+        return dims * math.log(spec.original / (2.0 * math.pi * t)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(turn(spec.fast)), 0)
+    hi = min(math.ceil(turn(spec.slow)), dims - 1)
+    ramp = np.clip((np.arange(dims // 2, dtype=np.float64) - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return f / spec.factor * ramp + f * (1.0 - ramp), 0.1 * math.log(spec.factor) + 1.0
+
+
+class RampRotary(PositionEncoding):
+    """Rotary encoding with frequencies stretched along a ramp (ScaledRotarySpec). It only owns the tables:
+    angles and their cos / sin in float64 on the host, the multiplier folded in, rounded to float32
+    [max_positions, dims / 2]; the mixer that names it rotates inside its own kernels."""
+
+    def __init__(self, spec: ScaledRotarySpec, env):
+        super().__init__(spec, env)
+        if spec.dims < 0 or spec.dims % 2:
+            raise ValueError(f"rotary position encoding needs an even number of dimensions, got {spec.dims}")
+        if spec.max_positions <= 0:
+            raise ValueError("rotary position encoding needs max_positions >= 1")
+        if spec.factor > 0 and not (spec.original > 0 and spec.fast > 0 and spec.slow > 0 and spec.base > 1):
+            raise ValueError("rotary frequency ramp: original, fast and slow must be positive and base > 1")
+        self.cos = self.sin = None
+        if spec.dims:
+            key = (spec, str(env.device))
+            hit = _TABLES.get(key)
+            if hit is None:
+                f, m = ramp_frequencies(spec)
+                ang = np.arange(spec.max_positions, dtype=np.float64)[:, None] * f[None, :]
+                hit = (torch.from_numpy((np.cos(ang) * m).astype(np.float32)).to(env.device),
+                       torch.from_numpy((np.sin(ang) * m).astype(np.float32)).to(env.device))
+                while len(_TABLES) >= 8:
+                    _TABLES.pop(next(iter(_TABLES)))
+                _TABLES[key] = hit
+            self.cos, self.sin = hit
+
+    def rotation_tables(self):
+        return self.cos, self.sin
+
+
 class NoPosition(PositionEncoding):
     takes_partial_sums = True
 
@@ -108,3 +155,4 @@ class NoPosition(PositionEncoding):
 
 register_part("position", "rope", RotaryPosition)
 register_part("position", "none", NoPosition)
+register_part("position", "rope_ramp", RampRotary)

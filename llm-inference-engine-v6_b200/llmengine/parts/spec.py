@@ -50,6 +50,52 @@ class PositionSpec:
 
 
 @dataclass(frozen=True)
+class ScaledRotarySpec:
+    """kind "rope_ramp": rotary, half-split layout over the first `dims` numbers of the vector it is given.
+    Pair i turns by position * f_i, f_i = base^(-2i/dims). With factor > 0 the frequencies are stretched
+    along a ramp: turn(t) = dims * ln(original / (2 pi t)) / (2 ln base), lo = max(floor(turn(fast)), 0),
+    hi = min(ceil(turn(slow)), dims - 1), ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1),
+    f_i <- f_i / factor * ramp_i + f_i * (1 - ramp_i), and cos and sin are both multiplied by
+    0.1 ln(factor) + 1. factor 0: plain frequencies, no multiplier."""
+    kind: str
+    dims: int
+    base: float
+    max_positions: int
+    factor: float = 0.0
+    original: float = 0.0
+    fast: float = 0.0
+    slow: float = 0.0
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal attention whose keys and values are maps of one cached latent per token (parts/latent_attention.py).
+    heads H; per head `dim` unrotated and `rot_dim` rotated query/key numbers and `vdim` value numbers;
+    `kv_rank` the latent of keys and values, `q_rank` the latent of queries. `scale` multiplies the scores as given."""
+    kind: str
+    hidden: int
+    heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    kv_rank: int
+    q_rank: int
+    scale: float
+    eps: float
+    position: object  # a position spec with rotation tables over `dims` <= rot_dim numbers
+    dq_weight: str
+    dq_norm: str
+    uq_weight: str
+    dkv_weight: str
+    dkv_norm: str
+    uk_weight: str
+    uv_weight: str
+    gate_weight: str
+    o_weight: str
+    window: int = 0
+
+
+@dataclass(frozen=True)
 class AttentionSpec:
     """Causal grouped-query attention. window = 0 keeps every key; W > 0 reads the last W."""
     kind: str
@@ -75,26 +121,65 @@ class GatedMLPSpec:
     gate_weight: str
     up_weight: str
     down_weight: str
-    activation: str = "silu"
+    activation: str = "silu"  # or "gelu_tanh"
+
+
+@dataclass(frozen=True)
+class RoutedMLPSpec:
+    """Mixture of experts: logits = router x + router_bias in float32; each token uses the `top` experts with the largest
+    logits, weighted by the softmax over the chosen logits; an expert is down_e(act(up_e(x))) without biases.
+    up_weights / down_weights: one checkpoint name per expert. activation "gelu" (the exact, erf form)."""
+    kind: str
+    hidden: int
+    intermediate: int
+    experts: int
+    top: int
+    router_weight: str
+    router_bias: Optional[str]
+    up_weights: Tuple[str, ...]
+    down_weights: Tuple[str, ...]
+    activation: str = "gelu"
+
+
+@dataclass(frozen=True)
+class TokenSideSpec:
+    """A per-layer input from the token itself, added after the layer: e = table[token, col0 : col0 + dim];
+    y = proj(gelu_tanh(gate(x)) * e) for the stream x; x += y / rms(y) * norm (eps inside the root)."""
+    kind: str
+    hidden: int
+    dim: int
+    vocab_size: int
+    table: str       # [vocab, table_width], shared by all layers
+    table_width: int
+    col0: int
+    gate_weight: str  # [dim, hidden]
+    proj_weight: str  # [hidden, dim]
+    norm_weight: str  # [hidden]
+    eps: float
 
 
 @dataclass(frozen=True)
 class BlockSpec:
     """kind "pre_norm": h += mixer(norm1(h)); h += feed_forward(norm2(h)).
-    mixer / feed_forward are any registered spec objects with a `kind`."""
+    kind "parallel": h += mixer(norm1(h)) + feed_forward(norm2(h)), both of the same h (feed_forward and norm2 may be
+    None: then the mixer alone); then, if `token_input` is given, h += token_input(h, tokens).
+    mixer / feed_forward / token_input are any registered spec objects with a `kind`."""
     kind: str
     norm1: object
     mixer: object
     norm2: object
     feed_forward: object
+    token_input: object = None
 
 
 @dataclass(frozen=True)
 class LayerRun:
     """One entry of the execution order: run `layer`; if `cache_from` names another layer, this
-    run reads that layer's cache and writes none of its own."""
+    run reads that layer's cache and writes none of its own. add_embedding: the embedding's output
+    (the stream as it was before the first run) is added to the stream right before this run."""
     layer: int
     cache_from: Optional[int] = None
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)

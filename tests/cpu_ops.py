@@ -45,7 +45,13 @@ class CpuOps:
         h[:n] += d[:n]
         return h
 
-    def silu_mul(self, gate_up, out, block=0):
+    @staticmethod
+    def _act(g, act):
+        if act == "gelu_tanh":
+            return 0.5 * g * (1.0 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
+        return g / (1.0 + torch.exp(-g))
+
+    def silu_mul(self, gate_up, out, block=0, act="silu"):
         ff = out.shape[1]
         if block:
             gu = gate_up.float().view(gate_up.shape[0], ff // block, 2, block)
@@ -53,7 +59,7 @@ class CpuOps:
         else:
             g = gate_up[:, :ff].float()
             u = gate_up[:, ff:].float()
-        out.copy_(((g / (1.0 + torch.exp(-g))) * u).to(out.dtype))
+        out.copy_((self._act(g, act) * u).to(out.dtype))
         return out
 
     def gemm(self, a, w, out, ws=None):
@@ -71,12 +77,136 @@ class CpuOps:
         out.copy_(parts.sum(0).to(out.dtype))
         return out
 
-    def silu_mul_partials(self, parts, out, block=0):
-        return self.silu_mul(parts.sum(0), out, block)
+    def silu_mul_partials(self, parts, out, block=0, act="silu"):
+        return self.silu_mul(parts.sum(0), out, block, act)
 
-    def gemm_swiglu(self, a, w_blocked, out, ws=None):
+    def gemm_swiglu(self, a, w_blocked, out, ws=None, act="silu"):
         gate_up = (a.float() @ w_blocked.float().t())
-        return self.silu_mul(gate_up, out, 128)
+        return self.silu_mul(gate_up, out, 128, act)
+
+    # ------------------------------------------------------------------ stream, token side input
+    def stream_add(self, h, a, b=None, copy=None, n_rows=None):
+        n = h.shape[0] if n_rows is None else n_rows
+        for d in (a, b):
+            if d is not None:
+                h[:n] += (d if d.dim() == 2 else d.sum(0))[:n]
+        if copy is not None:
+            copy[:n] = h[:n].to(copy.dtype)
+        return h
+
+    def token_gate(self, z, table, col0, ids, out):
+        n, dim = out.shape
+        e = table[ids[:n].long(), col0:col0 + dim].float()
+        out.copy_((self._act(z.float(), "gelu_tanh") * e).to(out.dtype))
+        return out
+
+    # ------------------------------------------------------------------ latent attention
+    def latent_prep(self, parts, q_off, q_rank, kv_off, kv_rank, rot_dim, rot_dims, wq, wkv, eps, cos, sin, batch, block_table, cq, cache):
+        n = batch.n_tokens
+        x = parts.sum(0)[:n]
+        q = x[:, q_off:q_off + q_rank]
+        cq[:n] = (q / torch.sqrt((q * q).mean(-1, keepdim=True) + eps) * wq).to(cq.dtype)
+        if cache is None:
+            return
+        c = x[:, kv_off:kv_off + kv_rank]
+        c = c / torch.sqrt((c * c).mean(-1, keepdim=True) + eps) * wkv
+        kr = x[:, kv_off + kv_rank:kv_off + kv_rank + rot_dim].clone()
+        half, ps = rot_dims // 2, cache.shape[2]
+        for t in range(n):
+            pos = int(batch.positions[t])
+            if half:
+                u, v = kr[t, :half].clone(), kr[t, half:rot_dims].clone()
+                kr[t, :half] = u * cos[pos] - v * sin[pos]
+                kr[t, half:rot_dims] = v * cos[pos] + u * sin[pos]
+            page = int(block_table[int(batch.token_seq[t]), pos // ps])
+            assert page >= 0, "write into a page that was given back"
+            cache[page, 0, pos % ps] = torch.cat([c[t], kr[t]]).to(cache.dtype)
+
+    def heads_product(self, a, w, out, gate=None, gate_off=0):
+        y = torch.einsum("thk,hnk->thn", a.float(), w.float())
+        if gate is not None:
+            n, H, N = out.shape
+            g = gate.sum(0)[:n, gate_off:gate_off + H * N].view(n, H, N)
+            y = y * torch.sigmoid(g)
+        out.copy_(y.to(out.dtype))
+        return out
+
+    def latent_query(self, q, wkt, ql, heads, dim, rot_dim, kv_rank, rot_dims, cos, sin, positions, absorb=True):
+        n = ql.shape[0]
+        qh = q[:n].float().view(n, heads, dim + rot_dim)
+        if absorb:
+            ql[:, :, :kv_rank] = torch.einsum("thd,hrd->thr", qh[:, :, :dim], wkt.float()).to(ql.dtype)
+        r = qh[:, :, dim:].clone()
+        half = rot_dims // 2
+        if half:
+            pos = positions[:n].long()
+            c, s = cos[pos][:, None, :], sin[pos][:, None, :]
+            u, v = r[:, :, :half].clone(), r[:, :, half:rot_dims].clone()
+            r[:, :, :half] = u * c - v * s
+            r[:, :, half:rot_dims] = v * c + u * s
+        ql[:, :, kv_rank:] = r.to(ql.dtype)
+        return ql
+
+    def latent_attention(self, ql, cache, batch, block_table, out, kv_rank, scale, window=0):
+        ps = cache.shape[2]
+        for t in range(batch.n_tokens):
+            pos = int(batch.positions[t])
+            lo = max(0, pos - window + 1) if window > 0 else 0
+            idx = torch.arange(lo, pos + 1)
+            pages = block_table[int(batch.token_seq[t])][(idx // ps).long()].long()
+            assert (pages >= 0).all(), "read from a page that was given back"
+            rows = cache[pages, 0, (idx % ps).long(), :].float()  # [S, Dk]
+            p = torch.softmax((ql[t].float() @ rows.t()) * scale, dim=-1)  # [H, S]
+            out[t] = (p @ rows[:, :kv_rank]).to(out.dtype)
+        return out
+
+    def sigmoid_gate(self, x, gate, gate_off):
+        n, cols = x.shape
+        x.copy_((x.float() * torch.sigmoid(gate.sum(0)[:n, gate_off:gate_off + cols])).to(x.dtype))
+        return x
+
+    # ------------------------------------------------------------------ routed feed-forward
+    def route(self, x, w, bias, top, idx, share):
+        z = x.float() @ w.float().t()
+        if bias is not None:
+            z = z + bias
+        order = torch.argsort(z, dim=-1, descending=True, stable=True)[:, :top]
+        idx.copy_(order.to(torch.int32))
+        share.copy_(torch.softmax(torch.gather(z, 1, order), dim=-1))
+
+    def routed_tile_rows(self, n_tokens=0, dtype=None):
+        return 4
+
+    def routed_group(self, idx, experts, tile, ws, tag):
+        flat = idx.reshape(-1).tolist()
+        tiles_e, tiles_r = [], []
+        for e in range(experts):
+            rows = [p for p, ex in enumerate(flat) if ex == e]
+            for i in range(0, len(rows), tile):
+                chunk = rows[i:i + tile]
+                tiles_e.append(e)
+                tiles_r.append(chunk + [-1] * (tile - len(chunk)))
+        cap = (len(flat) + tile - 1) // tile + experts
+        while len(tiles_e) < cap:
+            tiles_e.append(-1)
+            tiles_r.append([-1] * tile)
+        return torch.tensor(tiles_e, dtype=torch.int32), torch.tensor(tiles_r, dtype=torch.int32)
+
+    def routed_product(self, a, a_div, w, tile_expert, tile_rows, out, epilogue, share=None):
+        for e, rows in zip(tile_expert.tolist(), tile_rows.tolist()):
+            if e < 0:
+                continue
+            for p in rows:
+                if p < 0:
+                    continue
+                v = w[e].float() @ a[p // a_div].float()
+                v = 0.5 * v * (1.0 + torch.erf(v / 2.0 ** 0.5)) if epilogue == "gelu" else v * share[p]
+                out[p] = v.to(out.dtype)
+        return out
+
+    def routed_combine(self, y, out, top):
+        out.copy_(y.view(out.shape[0], top, -1).sum(1))
+        return out
 
     def rope_kv_write(self, qkv, positions, token_seq, block_table, cos, sin, kcache, vcache, n_tokens, nq, nkv, hd, parts=None):
         half = hd // 2
