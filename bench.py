@@ -436,6 +436,119 @@ def run_reference(args):
     return 0
 
 
+# ------------------------------------------------------------------------------------------------ a design beside Llama
+def vapelix_sizes(width, heads, dim, rot_dim, vdim, kv_rank, q_rank, ff, experts, top, expert_ff, layers, vocab, side):
+    mixer = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank,
+             "scale": (dim + rot_dim) ** -0.5,
+             "rot": {"dims": rot_dim, "base": 10000.0, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}}
+    return {"architecture": "Vapelix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "max_positions": 8192,
+            "layers": [{"type": "latent_attention", "mixer": mixer, "mlp": dense if i == 0 else moe} for i in range(layers)],
+            "token_side": {"dim": side}}
+
+
+# name -> (Vapelix configuration, the Llama configuration of equal width, depth, heads and feed-forward rows a token)
+DESIGN_SIZES = {
+    "w1024": (vapelix_sizes(1024, 8, 64, 32, 64, 256, 384, 2816, 8, 2, 1408, 4, 32768, 64),
+              dict(GEOMETRY, hidden_size=1024, intermediate_size=2816, num_hidden_layers=4, num_attention_heads=16, num_key_value_heads=4,
+                   head_dim=64, vocab_size=32768, rope_scaling=None)),
+    "w2048": (vapelix_sizes(2048, 16, 128, 64, 128, 512, 768, 8192, 16, 4, 2048, 4, 32768, 128),
+              dict(GEOMETRY, hidden_size=2048, intermediate_size=8192, num_hidden_layers=4, num_attention_heads=32, num_key_value_heads=8,
+                   head_dim=64, vocab_size=32768, rope_scaling=None)),
+    "w4096": (vapelix_sizes(4096, 32, 128, 64, 128, 512, 1536, 14336, 32, 4, 3584, 2, 32768, 256),
+              dict(GEOMETRY, hidden_size=4096, intermediate_size=14336, num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8,
+                   head_dim=128, vocab_size=32768, rope_scaling=None)),
+}
+
+
+def run_design(args):
+    """Prompt and decode throughput of another design at sizes that resemble a real model's layers (random weights),
+    beside the Llama decoder of equal width, depth and feed-forward rows a token: one JSON line a size."""
+    import torch
+    import llmengine
+    from llmengine.cache import host_module
+    from llmengine.engine.graphs import DecodeGraphs
+
+    torch.cuda.set_device(0)
+    H = host_module()
+    K, W, B = args.steps, args.warmup, args.batch
+    gen = torch.Generator().manual_seed(1)
+
+    def measure(cfg, vocab):
+        with tempfile.TemporaryDirectory(prefix="llmengine_bench_") as tmp:
+            llmengine.write_random_model(tmp, cfg, seed=0, dtype=torch.bfloat16)
+            blocks = B * (CONTEXT + 2 * (K + W) + 128) // BLOCK_SIZE + PREFILL_TOKENS // BLOCK_SIZE + 8
+            eng = llmengine.Engine(tmp, "bf16", block_size=BLOCK_SIZE, num_blocks=blocks, max_concurrent=B, cuda_graphs=args.graphs)
+            eng.configure_cache()
+        pre = []
+        for i in range(W + max(2, min(K, 5))):
+            ids = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+            e, rid = H.StepEntries(), 10 ** 9 + i
+            eng.cm.add_request(rid)
+            assert eng.cm.reserve(rid, PREFILL_TOKENS)
+            e.add(rid, ids, [PREFILL_TOKENS - 1])
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            eng.step(e)
+            b.record()
+            torch.cuda.synchronize()
+            eng.cm.release(rid)
+            if i >= W:
+                pre.append(a.elapsed_time(b) / 1e3)
+        sch = llmengine.ContinuousBatchScheduler(eng, None, max_concurrent=B, max_prefill_tokens_per_step=PREFILL_TOKENS)
+        for _ in range(B):
+            sch.enqueue(torch.randint(0, vocab, (CONTEXT,), generator=gen).tolist(), 2 * (K + W) + B + 8)
+        for _ in range(2 * B + 8):
+            if sch.core.num_running == B:
+                break
+            sch.step()
+        assert sch.core.num_running == B, "the contexts could not be filled"
+
+        def one_step():
+            entries = sch.core.plan()
+            if eng.cuda_graphs:
+                if eng.graphs is None:
+                    eng.graphs = DecodeGraphs(eng)
+                eng.graphs.run_device(entries)
+            else:
+                ctx, logits = eng.step(entries)
+                eng.sampler.sample_device(logits, ctx, ctx.n_rows)
+            sch.core.commit([1] * len(entries))
+
+        for _ in range(W):
+            one_step()
+        torch.cuda.synchronize()
+        eng.ops.launches = 0
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(K):
+            one_step()
+        b.record()
+        torch.cuda.synchronize()
+        code = eng.ops.tensor_core_error()
+        if code:
+            raise RuntimeError(f"a tensor-core kernel gave up a wait (code {code})")
+        dec = a.elapsed_time(b) / 1e3 / K
+        return {"prefill_tokens_per_s": round(PREFILL_TOKENS / statistics.median(pre), 1), "prefill_ms": round(statistics.median(pre) * 1e3, 3),
+                "decode_tokens_per_s": round(B / dec, 1), "decode_ms_per_step": round(dec * 1e3, 4),
+                "launches_per_decode_step": round(eng.ops.launches / K, 1), "weight_bytes": eng.model.weight_bytes,
+                "cache_bytes_per_token": eng.model.kv_bytes_per_token()}
+
+    for name in (args.sizes.split(",") if args.sizes else sorted(DESIGN_SIZES)):
+        design_cfg, llama_cfg = DESIGN_SIZES[name]
+        clocks = ClockSampler()
+        clocks.start()
+        rec = {"bench": "design beside the closest existing model", "design": args.design, "sizes": name, "dtype": "bf16",
+               "data": "synthetic: random weights N(0,0.02), uniform random token ids", "batch": B, "context": CONTEXT,
+               "prefill_tokens": PREFILL_TOKENS, "steps": K, "warmup": W,
+               args.design: measure(design_cfg, design_cfg["vocab"]), "llama": measure(llama_cfg, llama_cfg["vocab_size"])}
+        rec["clocks"] = clocks.stop()
+        print(json.dumps(rec), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -452,6 +565,10 @@ def main():
     ap.add_argument("--workload", choices=["decode", "serve", "long"], default="decode",
                     help="decode: the contract's line (default). serve / long: the workloads of the 3B and 8B configurations, a line of their own")
     ap.add_argument("--budget", type=int, default=2048, help="serve: prompt tokens a step (max_prefill_tokens_per_step)")
+    ap.add_argument("--design", choices=["vapelix"], default=None,
+                    help="instead of the contract's line: prompt and decode throughput of this design at a few layer sizes, "
+                         "beside the Llama decoder of equal size (one JSON line a size)")
+    ap.add_argument("--sizes", default="", help="--design: comma list of " + ",".join(sorted(DESIGN_SIZES)) + " (default: all)")
     ap.add_argument("--reference-setup-limit", type=float, default=900.0, help="seconds the reference arm may spend filling contexts")
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
@@ -462,6 +579,8 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         return run_reference(args)
+    if args.design:
+        return run_design(args)
     if args.workload != "decode":
         return run_workload(args)
     return run_ours(args)

@@ -164,7 +164,15 @@ struct EpiArgs {
 // gate projection followed by the 128 matching rows of the up projection, so one accumulator tile
 // holds both; the epilogue writes silu(gate) * up, 128 columns per tile, and the 2x wider
 // intermediate never goes to memory.
-template <int BN, bool SWAP, typename TO, bool SWIGLU = false, int EPI = EPI_NONE>
+// The activation of the gate in a gate|up product's epilogue. SWIGLU 1: silu, g / (1 + exp(-g)); 2: the tanh form of
+// gelu, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))); 0: no gate (a plain product).
+template <int ACT>
+__device__ __forceinline__ float gate_act(float g) {
+  if (ACT == 2) return 0.5f * g * (1.0f + tanhf(0.79788456080286535588f * (g + 0.044715f * g * g * g)));
+  return g / (1.0f + expf(-g));
+}
+
+template <int BN, bool SWAP, typename TO, int SWIGLU = false, int EPI = EPI_NONE>
 __global__ void __launch_bounds__(128)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TO* __restrict__ out,
                    int RA, int RB, int k_tiles, int k_tiles_per_split, long long ldo, long long split_stride, int stages,
@@ -296,7 +304,7 @@ __global__ void __launch_bounds__(128)
         tmem_load16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, gv);
         tmem_load16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c0 + BN / 2), uv);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) gv[i] = (gv[i] / (1.0f + expf(-gv[i]))) * uv[i];
+        for (int i = 0; i < 16; ++i) gv[i] = gate_act<SWIGLU>(gv[i]) * uv[i];
         const int col0 = b_row0 / 2 + c0;  // column of the activation matrix [tokens, RB / 2]
         if (ra < RA && col0 < RB / 2) {
           TO* dst = o + (size_t)ra * ldo + col0;
@@ -407,7 +415,7 @@ __global__ void __launch_bounds__(128)
 // lane 0: TMA; warp 5 lane 0: tcgen05.mma. Waits are bounded as in the one-tile kernel.
 constexpr int PERSIST_THREADS = 192;
 
-template <typename TO, bool SWIGLU, int BN>
+template <typename TO, int SWIGLU, int BN>
 __global__ void __launch_bounds__(PERSIST_THREADS)
     gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                               TO* __restrict__ out, int RA, int RB, int k_tiles, long long ldo, int stages, int m_tiles,
@@ -548,7 +556,7 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
           tmem_load16(acc + (uint32_t)c0, gv);
           tmem_load16(acc + (uint32_t)(c0 + BN / 2), uv);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) gv[i] = (gv[i] / (1.0f + expf(-gv[i]))) * uv[i];
+          for (int i = 0; i < 16; ++i) gv[i] = gate_act<SWIGLU>(gv[i]) * uv[i];
           const int col0 = b_row0 / 2 + c0;  // column of the activation matrix [tokens, RB / 2]
           if (ra < RA && col0 < RB / 2) {
             TO* dst = out + (size_t)ra * ldo + col0;
@@ -642,7 +650,7 @@ __host__ __device__ constexpr uint32_t instr_desc_pair(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 
-template <typename TO, bool SWIGLU>
+template <typename TO, int SWIGLU>
 __global__ void __launch_bounds__(PERSIST_THREADS)
     gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TO* __restrict__ out,
                         int RA, int RB, int k_tiles, long long ldo, int stages, int mp_tiles, int n_tiles,
@@ -782,7 +790,7 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
           tmem_load16(acc + (uint32_t)c0, gv);
           tmem_load16(acc + (uint32_t)(c0 + BN / 2), uv);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) gv[i] = (gv[i] / (1.0f + expf(-gv[i]))) * uv[i];
+          for (int i = 0; i < 16; ++i) gv[i] = gate_act<SWIGLU>(gv[i]) * uv[i];
           const int col0 = b_row0 / 2 + c0;
           if (ra < RA && col0 < RB / 2) {
             TO* dst = out + (size_t)ra * ldo + col0;
@@ -821,7 +829,7 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
   cluster_sync_all();
 }
 
-template <typename TO, bool SWIGLU>
+template <typename TO, int SWIGLU>
 int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, int RB, int K, long long ldo, int n_sms,
                    cudaStream_t stream) {
   constexpr int STAGE_BYTES = A_BYTES + 128 * BK * 2;
@@ -844,7 +852,7 @@ int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int 
   return LLM_OK;
 }
 
-template <typename TO, bool SWIGLU, int BN = 256>
+template <typename TO, int SWIGLU, int BN = 256>
 int launch_tc_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, int RB, int K, long long ldo,
                          int n_sms, cudaStream_t stream, int add_into = 0) {
   constexpr int STAGE_BYTES = A_BYTES + BN * BK * 2;
@@ -908,7 +916,7 @@ inline bool prefer_pairs(int mode, int M, int N, int K, bool allow_192 = true) {
   return rounds_pair * 256 * 0.92f < (float)cost_single && rounds_pair * k_tiles >= 64;
 }
 
-template <int BN, bool SWAP, typename TO, bool SWIGLU = false, int EPI = EPI_NONE>
+template <int BN, bool SWAP, typename TO, int SWIGLU = false, int EPI = EPI_NONE>
 int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, int RB, int K, int splits, long long ldo,
               long long split_stride, int stages, cudaStream_t stream, const EpiArgs& epi = EpiArgs(), int add_into = 0) {
   constexpr int STAGE_BYTES = A_BYTES + BN * BK * 2;
@@ -1103,12 +1111,13 @@ extern "C" int llm_gemm_tc_scaled(const void* a, const void* w, float* out, int 
   return LLM_OK;
 }
 
-// act[m, c] = silu(g[m, c]) * u[m, c] with g | u = a . w^T, for w [2*FF, K] whose rows are blocks of
+// act[m, c] = f(g[m, c]) * u[m, c] (f: silu for act 0, the tanh gelu for act 1) with g | u = a . w^T, for w [2*FF, K] whose rows are blocks of
 // 128 gate rows followed by the 128 matching up rows (FF a multiple of 128). act: bf16 [M, FF].
-extern "C" int llm_gemm_tc_swiglu(const void* a, const void* w, void* act, int M, int FF, int K, long long lda, long long ldw,
-                                  long long ld_act, cudaStream_t stream) {
+extern "C" int llm_gemm_tc_swiglu(const void* a, const void* w, void* out_act, int M, int FF, int K, long long lda, long long ldw,
+                                  long long ld_act, int act, cudaStream_t stream) {
   if (M == 0 || FF == 0) return LLM_OK;
   LLM_REQUIRE(llm_gemm_tc_supported(a, w, M, 2 * FF, K, lda, ldw), "gemm_tc_swiglu: operands must be 16-byte aligned with K and row strides multiples of 8");
+  LLM_REQUIRE(act == 0 || act == 1, "gemm_tc_swiglu: unknown activation %d (0 silu, 1 tanh gelu)", act);
   LLM_REQUIRE(FF % 128 == 0, "gemm_tc_swiglu: the intermediate size %d must be a multiple of 128", FF);
   LLM_REQUIRE(error_word() != nullptr, "gemm_tc_swiglu: cannot allocate the error word");
   CUtensorMap ma, mb;
@@ -1116,14 +1125,19 @@ extern "C" int llm_gemm_tc_swiglu(const void* a, const void* w, void* act, int M
   const int form = llm_gemm_tc_form(M, 2 * FF, K, 1);
   if (form == FORM_PAIRS) {
     LLM_REQUIRE(tensor_map_for(w, 2 * FF, K, ldw, 128, &mb), "gemm_tc_swiglu: cuTensorMapEncodeTiled failed");
-    const int rc2 = launch_tc_pair<bf16, true>(ma, mb, act, M, 2 * FF, K, ld_act, sm_count(), stream);
+    const int rc2 = act == 1 ? launch_tc_pair<bf16, 2>(ma, mb, out_act, M, 2 * FF, K, ld_act, sm_count(), stream)
+                             : launch_tc_pair<bf16, 1>(ma, mb, out_act, M, 2 * FF, K, ld_act, sm_count(), stream);
     if (rc2 != LLM_OK) return rc2;
     LLM_CHECK_LAUNCH("gemm_tc_swiglu");
     return LLM_OK;
   }
-  const int rc = form == FORM_PERSISTENT_256
-                     ? launch_tc_persistent<bf16, true>(ma, mb, act, M, 2 * FF, K, ld_act, sm_count(), stream)
-                     : launch_tc<256, false, bf16, true>(ma, mb, act, M, 2 * FF, K, 1, ld_act, 0, 4, stream);
+  int rc;
+  if (act == 1)
+    rc = form == FORM_PERSISTENT_256 ? launch_tc_persistent<bf16, 2>(ma, mb, out_act, M, 2 * FF, K, ld_act, sm_count(), stream)
+                                     : launch_tc<256, false, bf16, 2>(ma, mb, out_act, M, 2 * FF, K, 1, ld_act, 0, 4, stream);
+  else
+    rc = form == FORM_PERSISTENT_256 ? launch_tc_persistent<bf16, 1>(ma, mb, out_act, M, 2 * FF, K, ld_act, sm_count(), stream)
+                                     : launch_tc<256, false, bf16, 1>(ma, mb, out_act, M, 2 * FF, K, 1, ld_act, 0, 4, stream);
   if (rc != LLM_OK) return rc;
   LLM_CHECK_LAUNCH("gemm_tc_swiglu");
   return LLM_OK;

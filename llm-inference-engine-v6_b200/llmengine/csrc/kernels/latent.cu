@@ -82,22 +82,62 @@ __global__ void latent_prep_kernel(const float* __restrict__ parts, int n_parts,
 // ------------------------------------------------------------------------------------ per-head products
 constexpr int HP_WARPS = 4, HP_TOKENS = 8;
 
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
 // One warp owns one output column n of one head for HP_TOKENS tokens: lanes stride over k (the weight
-// row is read once, coalesced), then a shuffle tree; the order of additions depends on K alone.
+// row is read once, coalesced; eight numbers a lane a step where rows are 16-byte aligned, else one), then a
+// shuffle tree; the order of additions depends on K and the alignment alone, never on the batch.
 template <typename T>
 __device__ __forceinline__ void warp_dots(const T* __restrict__ a, long long lda, const T* __restrict__ wrow, int K, int t0, int T_,
-                                          float (&acc)[HP_TOKENS]) {
+                                          float (&acc)[HP_TOKENS], bool vec) {
   const int lane = threadIdx.x & 31;
 #pragma unroll
   for (int i = 0; i < HP_TOKENS; ++i) acc[i] = 0.f;
-  for (int k = lane; k < K; k += 32) {
-    const float wv = to_f32(wrow[k]);
+  if (vec) {
+    for (int k = lane * 8; k < K; k += 256) {
+      float wv[8];
+      load8(wrow + k, wv);
 #pragma unroll
-    for (int i = 0; i < HP_TOKENS; ++i)
-      if (t0 + i < T_) acc[i] = fmaf(to_f32(a[(size_t)(t0 + i) * lda + k]), wv, acc[i]);
+      for (int i = 0; i < HP_TOKENS; ++i) {
+        if (t0 + i < T_) {
+          float av[8];
+          load8(a + (size_t)(t0 + i) * lda + k, av);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[i] = fmaf(av[e], wv[e], acc[i]);
+        }
+      }
+    }
+  } else {
+    for (int k = lane; k < K; k += 32) {
+      const float wv = to_f32(wrow[k]);
+#pragma unroll
+      for (int i = 0; i < HP_TOKENS; ++i)
+        if (t0 + i < T_) acc[i] = fmaf(to_f32(a[(size_t)(t0 + i) * lda + k]), wv, acc[i]);
+    }
   }
 #pragma unroll
   for (int i = 0; i < HP_TOKENS; ++i) acc[i] = warp_sum(acc[i]);
+}
+
+// Whether rows of K numbers at these addresses and strides (in elements) can be read 16 bytes at a time.
+template <typename T>
+__device__ __forceinline__ bool rows_vectorizable(const T* a, long long lda, long long lda_h, const T* w, long long ldw, int K) {
+  constexpr int per = 16 / sizeof(T);
+  return K % 8 == 0 && (reinterpret_cast<uintptr_t>(a) & 15u) == 0 && (reinterpret_cast<uintptr_t>(w) & 15u) == 0 && lda % per == 0 &&
+         lda_h % per == 0 && ldw % per == 0;
 }
 
 // out[t, h*ldo_h + n] = (sum_k a[t, h*lda_h + k] * w[(h*N + n), k]) (* sigmoid(sum_p gate[p][t][g_off + h*N + n]))
@@ -112,7 +152,7 @@ __global__ void __launch_bounds__(HP_WARPS * 32)
   const int n = blockIdx.x * HP_WARPS + warp, h = blockIdx.y, t0 = blockIdx.z * HP_TOKENS;
   if (n >= N) return;
   float acc[HP_TOKENS];
-  warp_dots<T>(a + (size_t)h * lda_h, lda, w + ((size_t)h * N + n) * ldw, K, t0, T_, acc);
+  warp_dots<T>(a + (size_t)h * lda_h, lda, w + ((size_t)h * N + n) * ldw, K, t0, T_, acc, rows_vectorizable(a, lda, lda_h, w, ldw, K));
   if (lane < HP_TOKENS && t0 + lane < T_) {
     float v = 0.f;
 #pragma unroll
@@ -142,7 +182,8 @@ __global__ void __launch_bounds__(HP_WARPS * 32)
   const size_t ldl = (size_t)H * (R + dr);
   if (n < R) {
     float acc[HP_TOKENS];
-    warp_dots<T>(q + (size_t)h * (dn + dr), ldq, wkt + ((size_t)h * R + n) * dn, dn, t0, T_, acc);
+    warp_dots<T>(q + (size_t)h * (dn + dr), ldq, wkt + ((size_t)h * R + n) * dn, dn, t0, T_, acc,
+                 rows_vectorizable(q, ldq, (long long)(dn + dr), wkt, (long long)dn, dn));
     if (lane < HP_TOKENS && t0 + lane < T_) {
       float v = 0.f;
 #pragma unroll

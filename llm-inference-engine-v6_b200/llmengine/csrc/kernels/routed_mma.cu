@@ -1,0 +1,134 @@
+// Per-expert products of the routed feed-forward on tensor cores (bfloat16 operands, float32 accumulators).
+//
+// The step's (token, choice) pairs arrive sorted by expert in tiles of 64 rows of one expert (routed.cu: group).
+// A CTA owns one tile of rows and 64 output columns: its A rows are gathered through the tile's row list (row =
+// pair / a_div of the operand), its B rows are 64 rows of the expert's matrix [N, K]. K is walked in blocks of 64
+// with cp.async through a ring of three stages in shared memory; four warps of 16 rows each (m16n8k16). Every output row is
+// written at its pair's own index; a row's sum depends on K alone, not on the rest of its tile.
+// Epilogue 0: the exact (erf) gelu, bfloat16 out; 1: times the pair's router weight, float32 out.
+#include "common.cuh"
+#include "mma_common.cuh"
+
+#include <cmath>
+
+namespace {
+
+constexpr int RM_ROWS = 64, RM_COLS = 64, RM_BK = 64, RM_LD = RM_BK + 8, RM_THREADS = 128, RM_STAGES = 3;
+constexpr size_t RM_SMEM = (size_t)RM_STAGES * (RM_ROWS + RM_COLS) * RM_LD * sizeof(bf16);
+
+template <typename TO, int EPI>
+__global__ void __launch_bounds__(RM_THREADS)
+    routed_product_mma_kernel(const bf16* __restrict__ a, long long lda, int a_div, const bf16* __restrict__ w, long long w_stride, int N,
+                              int K, const int* __restrict__ tile_expert, const int* __restrict__ tile_rows, TO* __restrict__ out,
+                              long long ldo, const float* __restrict__ share) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  bf16 (*a_s)[RM_ROWS][RM_LD] = reinterpret_cast<bf16 (*)[RM_ROWS][RM_LD]>(smem_raw);
+  bf16 (*w_s)[RM_COLS][RM_LD] = reinterpret_cast<bf16 (*)[RM_COLS][RM_LD]>(smem_raw + (size_t)RM_STAGES * RM_ROWS * RM_LD * sizeof(bf16));
+  __shared__ int rows_s[RM_ROWS];
+  dep_launch();
+  dep_wait();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int e = tile_expert[blockIdx.y];
+  if (e < 0) return;
+  const int n0 = blockIdx.x * RM_COLS;
+  if (tid < RM_ROWS) rows_s[tid] = tile_rows[(size_t)blockIdx.y * RM_ROWS + tid];
+  __syncthreads();
+  const bf16* we = w + (size_t)e * w_stride;
+
+  auto load = [&](int kt, int buf) {
+#pragma unroll
+    for (int i = 0; i < RM_ROWS * (RM_BK / 8) / RM_THREADS; ++i) {
+      const int c = tid + i * RM_THREADS, r = c / (RM_BK / 8), ch = c % (RM_BK / 8);
+      const int k = kt * RM_BK + ch * 8;
+      const int pair = rows_s[r];
+      const bool va = pair >= 0 && k < K;
+      cp_async16(&a_s[buf][r][ch * 8], a + (va ? (size_t)(pair / a_div) * lda + k : 0), va);
+      const bool vw = n0 + r < N && k < K;
+      cp_async16(&w_s[buf][r][ch * 8], we + (vw ? (size_t)(n0 + r) * K + k : 0), vw);
+    }
+  };
+
+  float acc[RM_COLS / 8][4];
+#pragma unroll
+  for (int j = 0; j < RM_COLS / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  const int k_tiles = (K + RM_BK - 1) / RM_BK;
+#pragma unroll
+  for (int st = 0; st < RM_STAGES - 1; ++st) {  // the ring's first stages
+    if (st < k_tiles) load(st, st);
+    cp_async_commit();
+  }
+  for (int kt = 0; kt < k_tiles; ++kt) {
+    const int buf = kt % RM_STAGES;
+    cp_async_wait<RM_STAGES - 2>();
+    __syncthreads();  // block kt has landed, and everyone is done with the stage that block kt + STAGES - 1 overwrites
+    if (kt + RM_STAGES - 1 < k_tiles) load(kt + RM_STAGES - 1, (kt + RM_STAGES - 1) % RM_STAGES);
+    cp_async_commit();
+#pragma unroll
+    for (int ks = 0; ks < RM_BK / 16; ++ks) {
+      uint32_t af[4];
+      ldmatrix_x4(af, &a_s[buf][warp * 16 + (lane % 16)][ks * 16 + (lane / 16) * 8]);
+#pragma unroll
+      for (int j2 = 0; j2 < RM_COLS / 16; ++j2) {
+        uint32_t b[4];
+        ldmatrix_x4(b, &w_s[buf][j2 * 16 + (lane % 8) + (lane / 16) * 8][ks * 16 + ((lane / 8) % 2) * 8]);
+        mma_bf16(acc[2 * j2], af, b[0], b[1]);
+        mma_bf16(acc[2 * j2 + 1], af, b[2], b[3]);
+      }
+    }
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int pair = rows_s[warp * 16 + lane / 4 + half * 8];
+    if (pair < 0) continue;
+    const float sc = EPI == 1 ? share[pair] : 1.0f;
+    TO* dst = out + (size_t)pair * ldo;
+#pragma unroll
+    for (int j = 0; j < RM_COLS / 8; ++j) {
+#pragma unroll
+      for (int el = 0; el < 2; ++el) {
+        const int n = n0 + j * 8 + 2 * (lane % 4) + el;
+        if (n >= N) continue;
+        float v = acc[j][2 * half + el];
+        if (EPI == 0) v = 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
+        else v *= sc;
+        dst[n] = from_f32<TO>(v);
+      }
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" int llm_routed_product_mma_rows() { return RM_ROWS; }
+
+// Whether the tensor-core kernel takes these operands: 16-byte aligned rows of K % 8 == 0.
+extern "C" int llm_routed_product_mma_supported(const void* a, long long lda, const void* w, int K) {
+  return K > 0 && K % 8 == 0 && lda % 8 == 0 && (reinterpret_cast<uintptr_t>(a) & 15u) == 0 && (reinterpret_cast<uintptr_t>(w) & 15u) == 0;
+}
+
+extern "C" int llm_routed_product_mma(const void* a, long long lda, int a_div, const void* w, int N, int K, const int* tile_expert,
+                                      const int* tile_rows, int max_tiles, void* out, long long ldo, int epilogue, const float* share,
+                                      cudaStream_t stream) {
+  if (max_tiles == 0) return LLM_OK;
+  LLM_REQUIRE(llm_routed_product_mma_supported(a, lda, w, K), "routed_product_mma: operands must be 16-byte aligned with K and the row stride multiples of 8");
+  LLM_REQUIRE(N > 0 && a_div > 0 && max_tiles > 0 && max_tiles <= 65535, "routed_product_mma: bad sizes");
+  LLM_REQUIRE(epilogue == 0 || (epilogue == 1 && share), "routed_product_mma: unknown epilogue %d", epilogue);
+  dim3 grid(ceil_div(N, RM_COLS), max_tiles);
+  const long long ws = (long long)N * K;
+  static bool raised = false;
+  if (!raised) {
+    LLM_REQUIRE(cudaFuncSetAttribute(routed_product_mma_kernel<bf16, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RM_SMEM) == cudaSuccess &&
+                cudaFuncSetAttribute(routed_product_mma_kernel<float, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RM_SMEM) == cudaSuccess,
+                "routed_product_mma: cannot raise the shared memory limit");
+    raised = true;
+  }
+  if (epilogue == 0)
+    launch_kernel(routed_product_mma_kernel<bf16, 0>, grid, RM_THREADS, RM_SMEM, stream, (const bf16*)a, lda, a_div, (const bf16*)w, ws, N, K,
+                  tile_expert, tile_rows, (bf16*)out, ldo, share);
+  else
+    launch_kernel(routed_product_mma_kernel<float, 1>, grid, RM_THREADS, RM_SMEM, stream, (const bf16*)a, lda, a_div, (const bf16*)w, ws, N, K,
+                  tile_expert, tile_rows, (float*)out, ldo, share);
+  LLM_CHECK_LAUNCH("routed_product_mma");
+  return LLM_OK;
+}

@@ -189,6 +189,10 @@ def run_step_timeline(args) -> dict:
                num_hidden_layers=args.layers, num_attention_heads=args.heads, num_key_value_heads=args.kv_heads,
                head_dim=args.head_dim, vocab_size=args.vocab, max_position_embeddings=max(4096, args.context + 512),
                rms_norm_eps=1e-5, rope_theta=500000.0, tie_word_embeddings=True)
+    if args.config:  # any registered architecture, from a config.json
+        with open(args.config) as f:
+            cfg = json.load(f)
+        args.vocab = int(cfg.get("vocab_size") or cfg.get("vocab"))
     B, ctx = args.batch, args.context
     from .ops import get_ops
     get_ops().few_token_products = args.few_token_products == "on"
@@ -277,6 +281,7 @@ def main(argv=None) -> int:
     t = sub.add_parser("step")
     t.add_argument("--batch", type=int, default=8); t.add_argument("--context", type=int, default=2048)
     t.add_argument("--prefill", action="store_true")
+    t.add_argument("--config", default="", help="a config.json of any registered architecture (default: Llama sizes from the flags below)")
     t.add_argument("--few-token-products", choices=["on", "off"], default="off",
                    help="decode steps: products that add their K pieces inside a cluster, norms and SiLU folded in (off, the "
                         "engine's default: partial sums in memory, added by norm and activation kernels)")

@@ -79,6 +79,8 @@ class CudaOps:
         self.tcgen05_attention = True  # prompt portions: attention on tcgen05 where the geometry allows it
         self.tma_decode_attention = True  # single decoded tokens: keys and values by TMA where the geometry allows it
         self.fused_decode_attention = True  # ... with the sum of the q|k|v parts, rotation and cache write in the same kernel
+        self.latent_tensor_cores = True  # latent attention on mma.sync where the geometry allows it (off: CUDA cores)
+        self.routed_tensor_cores = True  # per-expert products of a routed feed-forward on mma.sync (off: CUDA cores)
         # Steps of few tokens: products that add their K pieces themselves, with the norm before, the residual sum
         # and SiLU * up folded in (gemm_few_tokens). Off: measured on B200 (batch 8, 2,048-token contexts, 1B layer
         # sizes) such a step takes 1.15 ms with the pieces meeting inside clusters and 1.40 ms with them meeting in
@@ -117,6 +119,7 @@ class CudaOps:
             lib.llm_last_error.restype = ctypes.c_char_p
             if name == "tensorcore":
                 lib.llm_attention_mma_scratch_floats.restype = ctypes.c_longlong
+                lib.llm_latent_attention_scratch_floats.restype = ctypes.c_longlong
                 lib.llm_gemm_decode_scratch_floats.restype = ctypes.c_longlong
                 # "auto", "on" or "off" (see use_cta_pairs; for measurements, pairs are not safe to serve with)
                 pairs = os.environ.get("LLMENGINE_CTA_PAIRS", "").strip().lower()
@@ -225,7 +228,7 @@ class CudaOps:
                                      c_int(block), c_int(self.ACTIVATIONS[act]), _stream()), lib)
         return out
 
-    EPILOGUE_ACTIVATIONS = ("silu",)  # what the gate|up product applies in its own epilogue (gemm_swiglu)
+    EPILOGUE_ACTIVATIONS = ("silu", "gelu_tanh")  # what the gate|up product applies in its own epilogue (gemm_swiglu)
 
     def gemm_swiglu(self, a: torch.Tensor, w_blocked: torch.Tensor, out: torch.Tensor, ws=None,
                     row_scale: Optional[RowScale] = None, act: str = "silu") -> torch.Tensor:
@@ -242,7 +245,7 @@ class CudaOps:
             lib = self.lib("tensorcore")
             self._check(lib.llm_gemm_tc_swiglu(_ptr(a), _ptr(w_blocked), _ptr(out), c_int(m), c_int(ff), c_int(k),
                                                c_longlong(a.stride(0)), c_longlong(w_blocked.stride(0)),
-                                               c_longlong(out.stride(0)), _stream()), lib)
+                                               c_longlong(out.stride(0)), c_int(self.ACTIVATIONS[act]), _stream()), lib)
             return out
         assert ws is not None, "gemm_swiglu needs a workspace when it cannot fuse"
         if m <= self.SWAP_MAX_TOKENS:
@@ -863,12 +866,49 @@ class CudaOps:
         n, H, Dk = ql.shape
         assert ql.is_contiguous() and out.is_contiguous() and cache.is_contiguous() and block_table.is_contiguous()
         assert cache.shape[1] == 1 and cache.shape[3] == Dk and out.shape == (n, H, kv_rank) and n >= batch.n_tokens
+        if ql.dtype == torch.bfloat16 and self.tensor_cores and self.latent_tensor_cores:
+            lib = self.lib("tensorcore")
+            if lib.llm_latent_attention_mma_supported(c_int(H), c_int(kv_rank), c_int(Dk - kv_rank)):
+                n_splits, split_keys, scratch = 1, 256, None
+                if batch.max_new_tokens == 1 and batch.n_tokens == batch.n_seqs:
+                    n_splits, split_keys = self._latent_split_policy(batch.n_seqs * -(-H // 32), batch.max_seq_len)
+                if n_splits > 1:
+                    floats = int(lib.llm_latent_attention_scratch_floats(c_int(batch.n_tokens), c_int(H), c_int(kv_rank), c_int(n_splits)))
+                    scratch = batch.ws.get("latent.splits", (floats,), torch.float32)
+                self._check(lib.llm_latent_attention_mma(
+                    _ptr(ql), _ptr(cache), _ptr(batch.seq_start), _ptr(batch.seq_ntok), _ptr(batch.seq_qoff), _ptr(block_table),
+                    c_int(block_table.shape[1]), _ptr(out), c_int(batch.n_seqs), c_int(batch.n_tokens), c_int(batch.max_new_tokens),
+                    c_int(H), c_int(kv_rank), c_int(Dk - kv_rank), c_int(cache.shape[2]), c_float(scale), c_int(window),
+                    c_int(n_splits), c_int(split_keys), _ptr(scratch), _stream()), lib)
+                if n_splits > 1:
+                    self.launches += 1  # the kernel that merges the splits
+                return out
         lib = self.lib()
         self._check(lib.llm_latent_attention_simt(_ptr(ql), _ptr(cache), c_int(dtype_code(ql.dtype)), _ptr(batch.positions),
                                                   _ptr(batch.token_seq), _ptr(block_table), c_int(block_table.shape[1]), _ptr(out),
                                                   c_int(batch.n_tokens), c_int(H), c_int(kv_rank), c_int(Dk - kv_rank),
                                                   c_int(cache.shape[2]), c_float(scale), c_int(window), _stream()), lib)
         return out
+
+    LATENT_TARGET_CTAS = 296  # two CTAs of the latent attention kernel on each of the 148 SMs
+    LATENT_MIN_SPLIT_KEYS = 128
+
+    def _latent_split_policy(self, ctas: int, max_seq_len: int):
+        """-> (number of key splits, keys per split) of a step of single tokens whose latent attention would run as
+        `ctas` CTAs without a split: the key range is cut (at absolute multiples of 64) until about LATENT_TARGET_CTAS
+        CTAs stream the cache, but into pieces of at least LATENT_MIN_SPLIT_KEYS keys."""
+        want = min(128, self.LATENT_TARGET_CTAS // max(ctas, 1), max_seq_len // self.LATENT_MIN_SPLIT_KEYS)
+        if want <= 1:
+            return 1, 256
+        split_keys = -(-(-(-max_seq_len // want)) // 64) * 64
+        return -(-max_seq_len // split_keys), split_keys
+
+    def latent_attention_kernel(self, heads: int, kv_rank: int, rot_dim: int, page: int) -> str:
+        """What latent attention of this geometry runs on in bfloat16: "tensor cores" or "CUDA cores"."""
+        if self.tensor_cores and self.latent_tensor_cores and self.lib("tensorcore").llm_latent_attention_mma_supported(
+                c_int(heads), c_int(kv_rank), c_int(rot_dim)):
+            return "tensor cores"
+        return "CUDA cores"
 
     def sigmoid_gate(self, x: torch.Tensor, gate: torch.Tensor, gate_off: int) -> torch.Tensor:
         """x[t, j] *= sigmoid(sum_p gate[p, t, gate_off + j]); gate float32 partial sums [p, n, width]."""
@@ -898,8 +938,11 @@ class CudaOps:
         self._check(lib.llm_route(_ptr(x), c_longlong(x.stride(0)), _ptr(w), _ptr(bias), c_int(n), c_int(D), c_int(E), c_int(top),
                                   _ptr(idx), _ptr(share), c_int(dtype_code(x.dtype)), _stream()), lib)
 
-    def routed_tile_rows(self, n_tokens: int = 0, dtype: Optional[torch.dtype] = None) -> int:
-        """Rows of a tile of the per-expert products."""
+    def routed_tile_rows(self, n_tokens: int = 0, dtype: Optional[torch.dtype] = None, inner=()) -> int:
+        """Rows of a tile of the per-expert products: the tensor-core kernel's in bfloat16 when every product's inner
+        size (`inner`) is a multiple of 8, else the CUDA-core kernel's."""
+        if dtype == torch.bfloat16 and self.tensor_cores and self.routed_tensor_cores and inner and all(k % 8 == 0 for k in inner):
+            return int(self.lib("tensorcore").llm_routed_product_mma_rows())
         return int(self.lib().llm_routed_product_rows())
 
     def routed_group(self, idx: torch.Tensor, experts: int, tile: int, ws, tag: str):
@@ -921,9 +964,19 @@ class CudaOps:
         the exact (erf) gelu; "share": times share[p] (float32, flat)."""
         _need(a, "routed_product.a"); _need(w, "routed_product.w", a.dtype); _need(out, "routed_product.out")
         E, N, K = w.shape
-        assert w.is_contiguous() and a.shape[1] == K and out.shape[1] == N and tile_rows.shape[1] == self.routed_tile_rows()
+        assert w.is_contiguous() and a.shape[1] == K and out.shape[1] == N
         if epilogue == "share":
             _need(share, "routed_product.share", torch.float32)
+        if a.dtype == torch.bfloat16 and self.tensor_cores and tile_rows.shape[1] != self.routed_tile_rows():
+            lib = self.lib("tensorcore")  # tiles made for the tensor-core kernel
+            assert tile_rows.shape[1] == int(lib.llm_routed_product_mma_rows())
+            assert out.dtype == (torch.bfloat16 if epilogue == "gelu" else torch.float32)
+            self._check(lib.llm_routed_product_mma(_ptr(a), c_longlong(a.stride(0)), c_int(a_div), _ptr(w), c_int(N), c_int(K),
+                                                   _ptr(tile_expert), _ptr(tile_rows), c_int(tile_expert.numel()), _ptr(out),
+                                                   c_longlong(out.stride(0)), c_int({"gelu": 0, "share": 1}[epilogue]), _ptr(share),
+                                                   _stream()), lib)
+            return out
+        assert tile_rows.shape[1] == self.routed_tile_rows()
         lib = self.lib()
         self._check(lib.llm_routed_product(_ptr(a), c_longlong(a.stride(0)), c_int(a_div), _ptr(w), c_int(N), c_int(K), _ptr(tile_expert),
                                            _ptr(tile_rows), c_int(tile_expert.numel()), _ptr(out), c_longlong(out.stride(0)),

@@ -55,7 +55,7 @@ class RoutedMLP(FeedForward):
         idx = ctx.ws.get("routed.idx", (n, s.top), torch.int32)
         share = ctx.ws.get("routed.share", (n, s.top), torch.float32)
         ops.route(x, self.router, self.bias, s.top, idx, share)
-        tile = ops.routed_tile_rows(n, dt)
+        tile = ops.routed_tile_rows(n, dt, (s.hidden, s.intermediate))
         tile_expert, tile_rows = ops.routed_group(idx, s.experts, tile, ctx.ws, "routed")
         act = ctx.ws.get("routed.act", (n * s.top, s.intermediate), dt)
         ops.routed_product(x, s.top, self.w_up, tile_expert, tile_rows, act, "gelu")
