@@ -21,8 +21,14 @@
 namespace {
 
 __device__ __forceinline__ float sum_parts(const float* __restrict__ parts, int n_parts, size_t pstride, size_t i) {
-  float x = parts[i];
-  for (int p = 1; p < n_parts; ++p) x += parts[(size_t)p * pstride + i];  // index order
+  float x = 0.f;
+  for (int p0 = 0; p0 < n_parts; p0 += 4) {  // four parts' loads in flight, added in index order
+    float v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] = p0 + k < n_parts ? parts[(size_t)(p0 + k) * pstride + i] : 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) x += v[k];
+  }
   return x;
 }
 

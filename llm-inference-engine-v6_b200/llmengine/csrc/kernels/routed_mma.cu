@@ -6,6 +6,7 @@
 // with cp.async through a ring of three stages in shared memory; four warps of 16 rows each (m16n8k16). Every output row is
 // written at its pair's own index; a row's sum depends on K alone, not on the rest of its tile.
 // Epilogue 0: the exact (erf) gelu, bfloat16 out; 1: times the pair's router weight, float32 out.
+// heads_product_mma: the same tile loop for a product per head over all tokens (the key and value maps of latent attention).
 #include "common.cuh"
 #include "mma_common.cuh"
 
@@ -98,6 +99,88 @@ __global__ void __launch_bounds__(RM_THREADS)
   }
 }
 
+// The same main loop for a product per head over ALL tokens: out[t, h, :] = w[h] a[t, h, :] (a rows lda apart, a head's
+// columns lda_h apart; out likewise), optionally times sigmoid of a gate given as float32 partial sums
+// [parts, tokens, gwidth] at columns g_off + h * N + n. grid (N / 64, tokens / 64, heads).
+__global__ void __launch_bounds__(RM_THREADS)
+    heads_product_mma_kernel(const bf16* __restrict__ a, long long lda, long long lda_h, const bf16* __restrict__ w, int T_, int N, int K,
+                             bf16* __restrict__ out, long long ldo, long long ldo_h, const float* __restrict__ gate, int n_parts,
+                             size_t pstride, int gwidth, int g_off) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  bf16 (*a_s)[RM_ROWS][RM_LD] = reinterpret_cast<bf16 (*)[RM_ROWS][RM_LD]>(smem_raw);
+  bf16 (*w_s)[RM_COLS][RM_LD] = reinterpret_cast<bf16 (*)[RM_COLS][RM_LD]>(smem_raw + (size_t)RM_STAGES * RM_ROWS * RM_LD * sizeof(bf16));
+  dep_launch();
+  dep_wait();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int h = blockIdx.z, t0 = blockIdx.y * RM_ROWS, n0 = blockIdx.x * RM_COLS;
+  const bf16* ah = a + (size_t)h * lda_h;
+  const bf16* wh = w + (size_t)h * N * K;
+
+  auto load = [&](int kt, int buf) {
+#pragma unroll
+    for (int i = 0; i < RM_ROWS * (RM_BK / 8) / RM_THREADS; ++i) {
+      const int c = tid + i * RM_THREADS, r = c / (RM_BK / 8), ch = c % (RM_BK / 8);
+      const int k = kt * RM_BK + ch * 8;
+      const bool va = t0 + r < T_ && k < K;
+      cp_async16(&a_s[buf][r][ch * 8], ah + (va ? (size_t)(t0 + r) * lda + k : 0), va);
+      const bool vw = n0 + r < N && k < K;
+      cp_async16(&w_s[buf][r][ch * 8], wh + (vw ? (size_t)(n0 + r) * K + k : 0), vw);
+    }
+  };
+
+  float acc[RM_COLS / 8][4];
+#pragma unroll
+  for (int j = 0; j < RM_COLS / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  const int k_tiles = (K + RM_BK - 1) / RM_BK;
+#pragma unroll
+  for (int st = 0; st < RM_STAGES - 1; ++st) {
+    if (st < k_tiles) load(st, st);
+    cp_async_commit();
+  }
+  for (int kt = 0; kt < k_tiles; ++kt) {
+    const int buf = kt % RM_STAGES;
+    cp_async_wait<RM_STAGES - 2>();
+    __syncthreads();
+    if (kt + RM_STAGES - 1 < k_tiles) load(kt + RM_STAGES - 1, (kt + RM_STAGES - 1) % RM_STAGES);
+    cp_async_commit();
+#pragma unroll
+    for (int ks = 0; ks < RM_BK / 16; ++ks) {
+      uint32_t af[4];
+      ldmatrix_x4(af, &a_s[buf][warp * 16 + (lane % 16)][ks * 16 + (lane / 16) * 8]);
+#pragma unroll
+      for (int j2 = 0; j2 < RM_COLS / 16; ++j2) {
+        uint32_t b[4];
+        ldmatrix_x4(b, &w_s[buf][j2 * 16 + (lane % 8) + (lane / 16) * 8][ks * 16 + ((lane / 8) % 2) * 8]);
+        mma_bf16(acc[2 * j2], af, b[0], b[1]);
+        mma_bf16(acc[2 * j2 + 1], af, b[2], b[3]);
+      }
+    }
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int t = t0 + warp * 16 + lane / 4 + half * 8;
+    if (t >= T_) continue;
+    bf16* dst = out + (size_t)t * ldo + (size_t)h * ldo_h;
+#pragma unroll
+    for (int j = 0; j < RM_COLS / 8; ++j) {
+#pragma unroll
+      for (int el = 0; el < 2; ++el) {
+        const int n = n0 + j * 8 + 2 * (lane % 4) + el;
+        if (n >= N) continue;
+        float v = acc[j][2 * half + el];
+        if (gate) {
+          const size_t gi = (size_t)t * gwidth + g_off + (size_t)h * N + n;
+          float g = gate[gi];
+          for (int q = 1; q < n_parts; ++q) g += gate[(size_t)q * pstride + gi];  // index order
+          v *= 1.0f / (1.0f + expf(-g));
+        }
+        dst[n] = __float2bfloat16_rn(v);
+      }
+    }
+  }
+}
+
 }  // namespace
 
 extern "C" int llm_routed_product_mma_rows() { return RM_ROWS; }
@@ -130,5 +213,30 @@ extern "C" int llm_routed_product_mma(const void* a, long long lda, int a_div, c
     launch_kernel(routed_product_mma_kernel<float, 1>, grid, RM_THREADS, RM_SMEM, stream, (const bf16*)a, lda, a_div, (const bf16*)w, ws, N, K,
                   tile_expert, tile_rows, (float*)out, ldo, share);
   LLM_CHECK_LAUNCH("routed_product_mma");
+  return LLM_OK;
+}
+
+// Whether heads_product_mma takes these operands (all of bfloat16): 16-byte aligned rows and head offsets, K % 8 == 0.
+extern "C" int llm_heads_product_mma_supported(const void* a, long long lda, long long lda_h, const void* w, int K) {
+  return K > 0 && K % 8 == 0 && lda % 8 == 0 && lda_h % 8 == 0 && (reinterpret_cast<uintptr_t>(a) & 15u) == 0 &&
+         (reinterpret_cast<uintptr_t>(w) & 15u) == 0;
+}
+
+extern "C" int llm_heads_product_mma(const void* a, long long lda, long long lda_h, const void* w, void* out, long long ldo, long long ldo_h,
+                                     int n_tokens, int H, int N, int K, const float* gate, int n_parts, long long pstride, int gwidth,
+                                     int g_off, cudaStream_t stream) {
+  if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(llm_heads_product_mma_supported(a, lda, lda_h, w, K), "heads_product_mma: operands must be 16-byte aligned with K and the strides multiples of 8");
+  LLM_REQUIRE(n_tokens > 0 && H > 0 && N > 0 && H <= 65535 && ceil_div(n_tokens, RM_ROWS) <= 65535, "heads_product_mma: bad sizes");
+  static bool raised = false;
+  if (!raised) {
+    LLM_REQUIRE(cudaFuncSetAttribute(heads_product_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RM_SMEM) == cudaSuccess,
+                "heads_product_mma: cannot raise the shared memory limit");
+    raised = true;
+  }
+  dim3 grid(ceil_div(N, RM_COLS), ceil_div(n_tokens, RM_ROWS), H);
+  launch_kernel(heads_product_mma_kernel, grid, RM_THREADS, RM_SMEM, stream, (const bf16*)a, lda, lda_h, (const bf16*)w, n_tokens, N, K,
+                (bf16*)out, ldo, ldo_h, gate, n_parts, (size_t)pstride, gwidth, g_off);
+  LLM_CHECK_LAUNCH("heads_product_mma");
   return LLM_OK;
 }

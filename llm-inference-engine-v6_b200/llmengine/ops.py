@@ -316,19 +316,28 @@ class CudaOps:
                                       c_int(dtype_code(a.dtype)), c_int(dtype_code(out.dtype)), _stream()), lib)
         return out
 
-    def gemm_heads(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
-        """out[:, h, :] = a[:, h, :] @ w[h].T head by head on the tensor-core product (a [n, H, K], w [H, N, K], out
-        [n, H, N]; views whose last dimension is contiguous). False, with nothing done, when the operands are not
-        what that kernel takes (the caller then uses heads_product)."""
-        H = w.shape[0]
-        if a.dtype != torch.bfloat16 or not all(self._tc_usable(a[:, h], w[h]) for h in (0, H - 1)):
+    def gemm_heads(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None,
+                   gate_off: int = 0) -> bool:
+        """out[:, h, :] = a[:, h, :] @ w[h].T for all heads in one tensor-core launch (a [n, H, K], w [H, N, K], out
+        [n, H, N] bfloat16; views whose last dimension is contiguous); with gate (float32 partial sums [p, n, width]),
+        times sigmoid(sum_p gate[p, t, gate_off + h*N + j]). False, with nothing done, when the operands are not what
+        that kernel takes (the caller then uses heads_product)."""
+        if a.dtype != torch.bfloat16 or not self.tensor_cores or a.stride(2) != 1 or out.stride(2) != 1:
             return False
-        if out.data_ptr() % 16 or (out.stride(1) * 2) % 16 or (out.stride(0) * 2) % 16:
+        n, H, K = a.shape
+        N = w.shape[1]
+        assert w.shape == (H, N, K) and w.is_contiguous() and out.shape == (n, H, N) and w.dtype == a.dtype == out.dtype
+        lib = self.lib("tensorcore")
+        if not lib.llm_heads_product_mma_supported(_ptr(a), c_longlong(a.stride(0)), c_longlong(a.stride(1)), _ptr(w), c_int(K)):
             return False
-        for h in range(H):
-            self._gemm_tc(a[:, h], w[h], out[:, h])
-            self.launches += 1
-        self.launches -= 1
+        gargs = (c_void_p(0), c_int(0), c_longlong(0), c_int(0), c_int(0))
+        if gate is not None:
+            _need(gate, "gemm_heads.gate", torch.float32)
+            assert gate.is_contiguous() and gate.dim() == 3 and gate.shape[1] >= n and gate_off + H * N <= gate.shape[2]
+            gargs = (_ptr(gate), c_int(gate.shape[0]), c_longlong(gate.stride(0)), c_int(gate.shape[2]), c_int(gate_off))
+        self._check(lib.llm_heads_product_mma(_ptr(a), c_longlong(a.stride(0)), c_longlong(a.stride(1)), _ptr(w), _ptr(out),
+                                              c_longlong(out.stride(0)), c_longlong(out.stride(1)), c_int(n), c_int(H), c_int(N), c_int(K),
+                                              *gargs, _stream()), lib)
         return True
 
     def gemm_partials(self, a: torch.Tensor, w: torch.Tensor, ws, tag: str) -> torch.Tensor:

@@ -105,17 +105,17 @@ class LatentAttention(Mixer):
         q = ctx.ws.get("latent.q", (n, H * (s.dim + s.rot_dim)), dt)
         ops.gemm(cq, self.w_uq, q, ctx.ws)
         ql = ctx.ws.get("latent.ql", (n, H, Dk), dt)
-        many = n > 64 and hasattr(ops, "gemm_heads")
+        many = n > 32 and hasattr(ops, "gemm_heads")
         if many and ops.gemm_heads(q.view(n, H, s.dim + s.rot_dim)[:, :, :s.dim], self.w_ukt, ql[:, :, :s.kv_rank]):
-            # a prompt-sized step: the heads' key maps as tensor-core products, head by head
+            # more than a few tokens: the heads' key maps as one tensor-core launch over tiles of tokens
             ops.latent_query(q, None, ql, H, s.dim, s.rot_dim, s.kv_rank, self.rot_dims, self.cos, self.sin, ctx.positions, absorb=False)
         else:
             ops.latent_query(q, self.w_ukt, ql, H, s.dim, s.rot_dim, s.kv_rank, self.rot_dims, self.cos, self.sin, ctx.positions)
         ol = ctx.ws.get("latent.ol", (n, H, s.kv_rank), dt)
         ops.latent_attention(ql, cache.k, ctx, ctx.block_tables[cache.group], ol, s.kv_rank, s.scale, s.window)
         att = ctx.ws.get("latent.out", (n, H * s.vdim), dt)
-        if many and ops.gemm_heads(ol, self.w_uv, att.view(n, H, s.vdim)):
-            ops.sigmoid_gate(att, parts, g_off)
+        if many and ops.gemm_heads(ol, self.w_uv, att.view(n, H, s.vdim), gate=parts, gate_off=g_off):
+            pass  # the heads' value maps and the output gate in one tensor-core launch
         else:
             ops.heads_product(ol, self.w_uv, att.view(n, H, s.vdim), gate=parts, gate_off=g_off)
         return add_into_stream_or_partials(ops, att, self.w_o, ctx, False, "latent.delta")
