@@ -213,6 +213,30 @@ __global__ void __launch_bounds__(HP_WARPS * 32)
   ql[(size_t)t * ldl + (size_t)h * (R + dr) + R + j] = from_f32<T>(v);
 }
 
+// The rotated part alone (the unrotated part's map runs elsewhere): a thread a number.
+template <typename T>
+__global__ void latent_query_rotate_kernel(const T* __restrict__ q, long long ldq, T* __restrict__ ql, int H, int dn, int dr, int R,
+                                           int rot_dims, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                           const int* __restrict__ positions, size_t total) {
+  dep_launch();
+  dep_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int j = (int)(i % dr);
+  const size_t th = i / dr;
+  const int h = (int)(th % H);
+  const size_t t = th / H;
+  const int half = rot_dims / 2;
+  const T* qr = q + t * ldq + (size_t)h * (dn + dr) + dn;
+  float v = to_f32(qr[j]);
+  if (j < rot_dims) {
+    const int pos = positions[t];
+    if (j < half) v = v * cos_t[(size_t)pos * half + j] - to_f32(qr[j + half]) * sin_t[(size_t)pos * half + j];
+    else v = v * cos_t[(size_t)pos * half + j - half] + to_f32(qr[j - half]) * sin_t[(size_t)pos * half + j - half];
+  }
+  ql[(t * H + h) * (size_t)(R + dr) + R + j] = from_f32<T>(v);
+}
+
 // ------------------------------------------------------------------------------------ attention
 constexpr int LA_WARPS = 4;
 
@@ -352,6 +376,20 @@ extern "C" int llm_latent_query(const void* q, long long ldq, const void* wkt, v
   LLM_REQUIRE(ceil_div(n_tokens, HP_TOKENS) <= 65535, "latent_query: %d tokens are too many for one launch", n_tokens);
   const int cols = (absorb ? R : 0) + dr;
   if (cols == 0) return LLM_OK;
+  if (!absorb) {
+    const size_t total = (size_t)n_tokens * H * dr;
+    const int blocks = ceil_div((long long)total, 256);
+    if (dtype == LLM_F32)
+      launch_kernel(latent_query_rotate_kernel<float>, blocks, 256, 0, stream, (const float*)q, ldq, (float*)ql, H, dn, dr, R, rot_dims, cos_t,
+                    sin_t, positions, total);
+    else if (dtype == LLM_BF16)
+      launch_kernel(latent_query_rotate_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)q, ldq, (bf16*)ql, H, dn, dr, R, rot_dims, cos_t,
+                    sin_t, positions, total);
+    else
+      LLM_REQUIRE(false, "latent_query: unknown dtype %d", dtype);
+    LLM_CHECK_LAUNCH("latent_query_rotate");
+    return LLM_OK;
+  }
   dim3 grid(ceil_div(cols, HP_WARPS), H, ceil_div(n_tokens, HP_TOKENS));
   if (dtype == LLM_F32)
     launch_kernel(latent_query_kernel<float>, grid, HP_WARPS * 32, 0, stream, (const float*)q, ldq, (const float*)wkt, (float*)ql, n_tokens, H,

@@ -21,7 +21,9 @@
 
 namespace {
 
-constexpr int LM_ROWS = 32, LM_KEYS = 64, LM_THREADS = 256, LM_CW = 4, LM_SLD = LM_KEYS + 4;
+constexpr int LM_CW = 4;  // column warps a group of rows
+constexpr int lm_rows(int rgs) { return 16 * rgs; }
+constexpr int lm_keys(int rgs) { return rgs == 4 ? 32 : 64; }
 
 struct LatentParams {
   const bf16* ql;     // [tokens, H, Dk]
@@ -33,9 +35,13 @@ struct LatentParams {
   float* part_o; float* part_ml; int split_keys, n_splits; long long n_tokens;
 };
 
-// DT: accumulator tiles of 16 columns a warp; R = 64 * DT.
-template <int DT, bool SPLIT>
-__global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(const LatentParams p) {
+// DT: accumulator tiles of 16 columns a warp; R = 64 * DT. RGS: groups of 16 rows a CTA. 2: 32 rows, key tiles of 64,
+// eight warps (steps of single tokens and short portions, and rows whose length is no multiple of 32). 4: 64 rows, key
+// tiles of 32, sixteen warps: the same shared memory holds twice the rows, so a fetched key row serves twice as many
+// queries and twice the warps hide one another's waits (prompt portions).
+template <int DT, bool SPLIT, int RGS>
+__global__ void __launch_bounds__(RGS * 128) latent_attention_mma_kernel(const LatentParams p) {
+  constexpr int LM_ROWS = 16 * RGS, LM_KEYS = RGS == 4 ? 32 : 64, LM_THREADS = RGS * 128, LM_SLD = LM_KEYS + 4;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   const int Dk = p.Dk, LD = Dk + 8, CH = Dk / 8;  // padded row; 16-byte chunks of a row
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);            // [LM_ROWS][LD]
@@ -47,8 +53,9 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(const 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rg = warp / LM_CW, cw = warp % LM_CW;
   const int seq = blockIdx.y;
-  const int htile = blockIdx.z % p.n_htiles, split = blockIdx.z / p.n_htiles;
-  const int gh = p.gh, tq_cap = LM_ROWS / gh;
+  const int gh = min(p.H, LM_ROWS), tq_cap = LM_ROWS / gh;  // heads a tile, tokens a tile
+  const int n_htiles = (p.H + gh - 1) / gh;
+  const int htile = blockIdx.z % n_htiles, split = blockIdx.z / n_htiles;
   const int head0 = htile * gh;
   const int ntok = p.seq_ntok[seq];
   const int q0 = blockIdx.x * tq_cap;
@@ -115,8 +122,8 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(const 
       __syncthreads();  // tile kt (and, the first time, the query rows) visible
       const bf16* kb = k_s + (size_t)buf * LM_KEYS * LD;
 
-      // ---- scores of this warp's 16 rows against its 16 keys, over all Dk numbers
-      {
+      // ---- scores of this warp's 16 rows against its share of the tile's keys, over all Dk numbers
+      if (LM_KEYS == 64) {  // 16 keys a warp: two accumulator tiles
         float s[2][4];
         s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
         const bf16* qrow = q_s + (rg * 16 + (lane % 16)) * LD + (lane / 16) * 8;
@@ -143,8 +150,32 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(const 
             s_s[row_b * LM_SLD + col] = vb ? s[j][2 + e] * sl2 : -INFINITY;
           }
         }
+      } else {  // 8 keys a warp: one ldmatrix brings the keys' numbers of two k-steps; even and odd steps sum apart
+        float se[4] = {0.f, 0.f, 0.f, 0.f}, so[4] = {0.f, 0.f, 0.f, 0.f};
+        const bf16* qrow = q_s + (rg * 16 + (lane % 16)) * LD + (lane / 16) * 8;
+        const bf16* krow = kb + (cw * 8 + (lane % 8)) * LD + (lane / 8) * 8;
+#pragma unroll 2
+        for (int ks = 0; ks < Dk / 16; ks += 2) {
+          uint32_t a0[4], a1[4], b[4];
+          ldmatrix_x4(a0, qrow + ks * 16);
+          ldmatrix_x4(a1, qrow + ks * 16 + 16);
+          ldmatrix_x4(b, krow + ks * 16);
+          mma_bf16(se, a0, b[0], b[1]);
+          mma_bf16(so, a1, b[2], b[3]);
+        }
+        const int col0 = cw * 8 + 2 * (lane % 4);
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int col = col0 + e;
+          const int key = kt * LM_KEYS + col;
+          const bool in_split = key >= lo && key <= hi;
+          const bool va = in_split && key <= pos_a && key >= lo_a;
+          const bool vb = in_split && key <= pos_b && key >= lo_b;
+          s_s[row_a * LM_SLD + col] = va ? (se[e] + so[e]) * sl2 : -INFINITY;
+          s_s[row_b * LM_SLD + col] = vb ? (se[2 + e] + so[2 + e]) * sl2 : -INFINITY;
+        }
       }
-      __syncthreads();  // all 64 scores of every row are there
+      __syncthreads();  // all scores of every row are there
 
       // ---- running softmax of rows a and b over the 64 keys (float32), then O += P V on this warp's columns
       float s2[LM_KEYS / 8][4];
@@ -281,19 +312,23 @@ __global__ void __launch_bounds__(LC_THREADS)
   }
 }
 
-size_t latent_smem(int Dk) { return (size_t)(LM_ROWS + 2 * LM_KEYS) * (Dk + 8) * sizeof(bf16) + (size_t)LM_ROWS * LM_SLD * sizeof(float); }
+size_t latent_smem(int Dk, int rgs = 2) {
+  return (size_t)(lm_rows(rgs) + 2 * lm_keys(rgs)) * (Dk + 8) * sizeof(bf16) + (size_t)lm_rows(rgs) * (lm_keys(rgs) + 4) * sizeof(float);
+}
+
+template <int DT, bool SPLIT, int RGS>
+int launch_latent_as(const LatentParams& p, dim3 grid, cudaStream_t stream) {
+  const size_t smem = latent_smem(p.Dk, RGS);
+  if (smem > 48 * 1024 && cudaFuncSetAttribute(latent_attention_mma_kernel<DT, SPLIT, RGS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return 1;
+  launch_kernel(latent_attention_mma_kernel<DT, SPLIT, RGS>, grid, RGS * 128, smem, stream, p);
+  return 0;
+}
 
 template <int DT>
-int launch_latent(const LatentParams& p, dim3 grid, bool split, cudaStream_t stream) {
-  const size_t smem = latent_smem(p.Dk);
-  if (split) {
-    if (smem > 48 * 1024 && cudaFuncSetAttribute(latent_attention_mma_kernel<DT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 1;
-    launch_kernel(latent_attention_mma_kernel<DT, true>, grid, LM_THREADS, smem, stream, p);
-  } else {
-    if (smem > 48 * 1024 && cudaFuncSetAttribute(latent_attention_mma_kernel<DT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 1;
-    launch_kernel(latent_attention_mma_kernel<DT, false>, grid, LM_THREADS, smem, stream, p);
-  }
-  return 0;
+int launch_latent(const LatentParams& p, dim3 grid, bool split, bool wide, cudaStream_t stream) {
+  if (split) return launch_latent_as<DT, true, 2>(p, grid, stream);
+  return wide ? launch_latent_as<DT, false, 4>(p, grid, stream) : launch_latent_as<DT, false, 2>(p, grid, stream);
 }
 
 }  // namespace
@@ -321,28 +356,31 @@ extern "C" int llm_latent_attention_mma(const void* ql, const void* cache, const
   LLM_REQUIRE((reinterpret_cast<uintptr_t>(ql) & 15u) == 0 && (reinterpret_cast<uintptr_t>(cache) & 15u) == 0,
               "latent_attention_mma: queries and cache must be 16-byte aligned");
   LLM_REQUIRE(n_splits <= LC_MAX_SPLITS, "latent_attention_mma: at most %d splits", LC_MAX_SPLITS);
-  LLM_REQUIRE(n_splits >= 1 && (n_splits == 1 || (split_keys > 0 && split_keys % LM_KEYS == 0 && scratch != nullptr && max_new_tokens == 1)),
+  LLM_REQUIRE(n_splits >= 1 && (n_splits == 1 || (split_keys > 0 && split_keys % 64 == 0 && scratch != nullptr && max_new_tokens == 1)),
               "latent_attention_mma: splits need single tokens, split_keys %% 64 == 0 and scratch");
   LatentParams p;
   p.ql = (const bf16*)ql; p.cache = (const bf16*)cache; p.seq_start = seq_start; p.seq_ntok = seq_ntok; p.seq_qoff = seq_qoff;
-  p.block_table = block_table; p.max_blocks = max_blocks; p.H = H; p.gh = H < LM_ROWS ? H : LM_ROWS;
+  // the wide form (64 rows a CTA) for steps with portions of at least 64 rows, where rows are a multiple of 32 numbers
+  const bool split = n_splits > 1;
+  const bool wide = !split && (long long)max_new_tokens * H >= 64 && (R + dr) % 32 == 0 && latent_smem(R + dr, 4) <= 220 * 1024;
+  const int rows = lm_rows(wide ? 4 : 2);
+  p.block_table = block_table; p.max_blocks = max_blocks; p.H = H; p.gh = H < rows ? H : rows;
   p.n_htiles = (H + p.gh - 1) / p.gh; p.R = R; p.Dk = R + dr; p.page_size = page_size; p.window = window; p.scale = scale;
   p.out = (bf16*)out; p.n_splits = n_splits; p.split_keys = split_keys; p.n_tokens = n_tokens;
   p.part_o = scratch; p.part_ml = scratch ? scratch + (size_t)n_splits * n_tokens * H * R : nullptr;
-  const int tq_cap = LM_ROWS / p.gh;
+  const int tq_cap = rows / p.gh;
   LLM_REQUIRE((long long)n_seqs <= 65535 && (long long)p.n_htiles * n_splits <= 65535, "latent_attention_mma: batch too large for the grid");
   dim3 grid((max_new_tokens + tq_cap - 1) / tq_cap, n_seqs, p.n_htiles * n_splits);
-  const bool split = n_splits > 1;
   int rc = 0;
   switch (R / 64) {
-    case 1: rc = launch_latent<1>(p, grid, split, stream); break;
-    case 2: rc = launch_latent<2>(p, grid, split, stream); break;
-    case 3: rc = launch_latent<3>(p, grid, split, stream); break;
-    case 4: rc = launch_latent<4>(p, grid, split, stream); break;
-    case 5: rc = launch_latent<5>(p, grid, split, stream); break;
-    case 6: rc = launch_latent<6>(p, grid, split, stream); break;
-    case 7: rc = launch_latent<7>(p, grid, split, stream); break;
-    default: rc = launch_latent<8>(p, grid, split, stream); break;
+    case 1: rc = launch_latent<1>(p, grid, split, wide, stream); break;
+    case 2: rc = launch_latent<2>(p, grid, split, wide, stream); break;
+    case 3: rc = launch_latent<3>(p, grid, split, wide, stream); break;
+    case 4: rc = launch_latent<4>(p, grid, split, wide, stream); break;
+    case 5: rc = launch_latent<5>(p, grid, split, wide, stream); break;
+    case 6: rc = launch_latent<6>(p, grid, split, wide, stream); break;
+    case 7: rc = launch_latent<7>(p, grid, split, wide, stream); break;
+    default: rc = launch_latent<8>(p, grid, split, wide, stream); break;
   }
   LLM_REQUIRE(rc == 0, "latent_attention_mma: cannot raise the shared memory limit");
   if (split) {

@@ -17,29 +17,34 @@ namespace {
 constexpr int RM_ROWS = 64, RM_COLS = 64, RM_BK = 64, RM_LD = RM_BK + 8, RM_THREADS = 128, RM_STAGES = 3;
 constexpr size_t RM_SMEM = (size_t)RM_STAGES * (RM_ROWS + RM_COLS) * RM_LD * sizeof(bf16);
 
-template <typename TO, int EPI>
-__global__ void __launch_bounds__(RM_THREADS)
+// WM 1: a tile of 64 rows x 64 columns, four warps of 16 x 64. WM 2 (many rows an expert): 128 x 128, eight warps of
+// 32 x 64 (four along the rows, two along the columns): six ldmatrix feed sixteen mma instead of five feeding eight,
+// and a row of the expert's matrix is fetched for twice as many rows.
+template <typename TO, int EPI, int WM>
+__global__ void __launch_bounds__(RM_THREADS * WM)
     routed_product_mma_kernel(const bf16* __restrict__ a, long long lda, int a_div, const bf16* __restrict__ w, long long w_stride, int N,
                               int K, const int* __restrict__ tile_expert, const int* __restrict__ tile_rows, TO* __restrict__ out,
                               long long ldo, const float* __restrict__ share) {
+  constexpr int ROWS = RM_ROWS * WM, COLS = RM_COLS * WM, THREADS = RM_THREADS * WM;
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  bf16 (*a_s)[RM_ROWS][RM_LD] = reinterpret_cast<bf16 (*)[RM_ROWS][RM_LD]>(smem_raw);
-  bf16 (*w_s)[RM_COLS][RM_LD] = reinterpret_cast<bf16 (*)[RM_COLS][RM_LD]>(smem_raw + (size_t)RM_STAGES * RM_ROWS * RM_LD * sizeof(bf16));
-  __shared__ int rows_s[RM_ROWS];
+  bf16 (*a_s)[ROWS][RM_LD] = reinterpret_cast<bf16 (*)[ROWS][RM_LD]>(smem_raw);
+  bf16 (*w_s)[COLS][RM_LD] = reinterpret_cast<bf16 (*)[COLS][RM_LD]>(smem_raw + (size_t)RM_STAGES * ROWS * RM_LD * sizeof(bf16));
+  __shared__ int rows_s[ROWS];
   dep_launch();
   dep_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int warp_m = warp % 4, warp_n = warp / 4;
   const int e = tile_expert[blockIdx.y];
   if (e < 0) return;
-  const int n0 = blockIdx.x * RM_COLS;
-  if (tid < RM_ROWS) rows_s[tid] = tile_rows[(size_t)blockIdx.y * RM_ROWS + tid];
+  const int n0 = blockIdx.x * COLS;
+  if (tid < ROWS) rows_s[tid] = tile_rows[(size_t)blockIdx.y * ROWS + tid];
   __syncthreads();
   const bf16* we = w + (size_t)e * w_stride;
 
   auto load = [&](int kt, int buf) {
 #pragma unroll
-    for (int i = 0; i < RM_ROWS * (RM_BK / 8) / RM_THREADS; ++i) {
-      const int c = tid + i * RM_THREADS, r = c / (RM_BK / 8), ch = c % (RM_BK / 8);
+    for (int i = 0; i < ROWS * (RM_BK / 8) / THREADS; ++i) {
+      const int c = tid + i * THREADS, r = c / (RM_BK / 8), ch = c % (RM_BK / 8);
       const int k = kt * RM_BK + ch * 8;
       const int pair = rows_s[r];
       const bool va = pair >= 0 && k < K;
@@ -49,9 +54,11 @@ __global__ void __launch_bounds__(RM_THREADS)
     }
   };
 
-  float acc[RM_COLS / 8][4];
+  float acc[WM][RM_COLS / 8][4];
 #pragma unroll
-  for (int j = 0; j < RM_COLS / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  for (int i = 0; i < WM; ++i)
+#pragma unroll
+    for (int j = 0; j < RM_COLS / 8; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
   const int k_tiles = (K + RM_BK - 1) / RM_BK;
 #pragma unroll
   for (int st = 0; st < RM_STAGES - 1; ++st) {  // the ring's first stages
@@ -66,34 +73,41 @@ __global__ void __launch_bounds__(RM_THREADS)
     cp_async_commit();
 #pragma unroll
     for (int ks = 0; ks < RM_BK / 16; ++ks) {
-      uint32_t af[4];
-      ldmatrix_x4(af, &a_s[buf][warp * 16 + (lane % 16)][ks * 16 + (lane / 16) * 8]);
+      uint32_t af[WM][4];
+#pragma unroll
+      for (int i = 0; i < WM; ++i) ldmatrix_x4(af[i], &a_s[buf][(warp_m * WM + i) * 16 + (lane % 16)][ks * 16 + (lane / 16) * 8]);
 #pragma unroll
       for (int j2 = 0; j2 < RM_COLS / 16; ++j2) {
         uint32_t b[4];
-        ldmatrix_x4(b, &w_s[buf][j2 * 16 + (lane % 8) + (lane / 16) * 8][ks * 16 + ((lane / 8) % 2) * 8]);
-        mma_bf16(acc[2 * j2], af, b[0], b[1]);
-        mma_bf16(acc[2 * j2 + 1], af, b[2], b[3]);
+        ldmatrix_x4(b, &w_s[buf][warp_n * RM_COLS + j2 * 16 + (lane % 8) + (lane / 16) * 8][ks * 16 + ((lane / 8) % 2) * 8]);
+#pragma unroll
+        for (int i = 0; i < WM; ++i) {
+          mma_bf16(acc[i][2 * j2], af[i], b[0], b[1]);
+          mma_bf16(acc[i][2 * j2 + 1], af[i], b[2], b[3]);
+        }
       }
     }
   }
   cp_async_wait<0>();
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int pair = rows_s[warp * 16 + lane / 4 + half * 8];
-    if (pair < 0) continue;
-    const float sc = EPI == 1 ? share[pair] : 1.0f;
-    TO* dst = out + (size_t)pair * ldo;
+  for (int i = 0; i < WM; ++i) {
 #pragma unroll
-    for (int j = 0; j < RM_COLS / 8; ++j) {
+    for (int half = 0; half < 2; ++half) {
+      const int pair = rows_s[(warp_m * WM + i) * 16 + lane / 4 + half * 8];
+      if (pair < 0) continue;
+      const float sc = EPI == 1 ? share[pair] : 1.0f;
+      TO* dst = out + (size_t)pair * ldo;
 #pragma unroll
-      for (int el = 0; el < 2; ++el) {
-        const int n = n0 + j * 8 + 2 * (lane % 4) + el;
-        if (n >= N) continue;
-        float v = acc[j][2 * half + el];
-        if (EPI == 0) v = 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
-        else v *= sc;
-        dst[n] = from_f32<TO>(v);
+      for (int j = 0; j < RM_COLS / 8; ++j) {
+#pragma unroll
+        for (int el = 0; el < 2; ++el) {
+          const int n = n0 + warp_n * RM_COLS + j * 8 + 2 * (lane % 4) + el;
+          if (n >= N) continue;
+          float v = acc[i][j][2 * half + el];
+          if (EPI == 0) v = 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
+          else v *= sc;
+          dst[n] = from_f32<TO>(v);
+        }
       }
     }
   }
@@ -183,35 +197,48 @@ __global__ void __launch_bounds__(RM_THREADS)
 
 }  // namespace
 
-extern "C" int llm_routed_product_mma_rows() { return RM_ROWS; }
+// Rows of a tile: 64, or 128 when an expert gets about that many rows or more.
+extern "C" int llm_routed_product_mma_rows(int rows_per_expert) { return rows_per_expert >= 96 ? 2 * RM_ROWS : RM_ROWS; }
 
 // Whether the tensor-core kernel takes these operands: 16-byte aligned rows of K % 8 == 0.
 extern "C" int llm_routed_product_mma_supported(const void* a, long long lda, const void* w, int K) {
   return K > 0 && K % 8 == 0 && lda % 8 == 0 && (reinterpret_cast<uintptr_t>(a) & 15u) == 0 && (reinterpret_cast<uintptr_t>(w) & 15u) == 0;
 }
 
+template <typename TO, int EPI, int WM>
+int launch_routed(dim3 grid, cudaStream_t stream, const void* a, long long lda, int a_div, const void* w, long long ws, int N, int K,
+                  const int* tile_expert, const int* tile_rows, void* out, long long ldo, const float* share) {
+  static bool raised = false;
+  if (!raised) {
+    if (cudaFuncSetAttribute(routed_product_mma_kernel<TO, EPI, WM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(RM_SMEM * WM)) != cudaSuccess)
+      return 1;
+    raised = true;
+  }
+  launch_kernel(routed_product_mma_kernel<TO, EPI, WM>, grid, RM_THREADS * WM, RM_SMEM * WM, stream, (const bf16*)a, lda, a_div, (const bf16*)w,
+                ws, N, K, tile_expert, tile_rows, (TO*)out, ldo, share);
+  return 0;
+}
+
+// tile: the rows of a tile of tile_rows (64 or 128, as llm_routed_product_mma_rows said when the pairs were grouped).
 extern "C" int llm_routed_product_mma(const void* a, long long lda, int a_div, const void* w, int N, int K, const int* tile_expert,
-                                      const int* tile_rows, int max_tiles, void* out, long long ldo, int epilogue, const float* share,
-                                      cudaStream_t stream) {
+                                      const int* tile_rows, int max_tiles, int tile, void* out, long long ldo, int epilogue,
+                                      const float* share, cudaStream_t stream) {
   if (max_tiles == 0) return LLM_OK;
   LLM_REQUIRE(llm_routed_product_mma_supported(a, lda, w, K), "routed_product_mma: operands must be 16-byte aligned with K and the row stride multiples of 8");
   LLM_REQUIRE(N > 0 && a_div > 0 && max_tiles > 0 && max_tiles <= 65535, "routed_product_mma: bad sizes");
+  LLM_REQUIRE(tile == RM_ROWS || tile == 2 * RM_ROWS, "routed_product_mma: tiles of %d rows (64 or 128)", tile);
   LLM_REQUIRE(epilogue == 0 || (epilogue == 1 && share), "routed_product_mma: unknown epilogue %d", epilogue);
-  dim3 grid(ceil_div(N, RM_COLS), max_tiles);
+  const int wm = tile / RM_ROWS;
+  dim3 grid(ceil_div(N, RM_COLS * wm), max_tiles);
   const long long ws = (long long)N * K;
-  static bool raised = false;
-  if (!raised) {
-    LLM_REQUIRE(cudaFuncSetAttribute(routed_product_mma_kernel<bf16, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RM_SMEM) == cudaSuccess &&
-                cudaFuncSetAttribute(routed_product_mma_kernel<float, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RM_SMEM) == cudaSuccess,
-                "routed_product_mma: cannot raise the shared memory limit");
-    raised = true;
-  }
+  int rc;
   if (epilogue == 0)
-    launch_kernel(routed_product_mma_kernel<bf16, 0>, grid, RM_THREADS, RM_SMEM, stream, (const bf16*)a, lda, a_div, (const bf16*)w, ws, N, K,
-                  tile_expert, tile_rows, (bf16*)out, ldo, share);
+    rc = wm == 2 ? launch_routed<bf16, 0, 2>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share)
+                 : launch_routed<bf16, 0, 1>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share);
   else
-    launch_kernel(routed_product_mma_kernel<float, 1>, grid, RM_THREADS, RM_SMEM, stream, (const bf16*)a, lda, a_div, (const bf16*)w, ws, N, K,
-                  tile_expert, tile_rows, (float*)out, ldo, share);
+    rc = wm == 2 ? launch_routed<float, 1, 2>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share)
+                 : launch_routed<float, 1, 1>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share);
+  LLM_REQUIRE(rc == 0, "routed_product_mma: cannot raise the shared memory limit");
   LLM_CHECK_LAUNCH("routed_product_mma");
   return LLM_OK;
 }

@@ -947,11 +947,12 @@ class CudaOps:
         self._check(lib.llm_route(_ptr(x), c_longlong(x.stride(0)), _ptr(w), _ptr(bias), c_int(n), c_int(D), c_int(E), c_int(top),
                                   _ptr(idx), _ptr(share), c_int(dtype_code(x.dtype)), _stream()), lib)
 
-    def routed_tile_rows(self, n_tokens: int = 0, dtype: Optional[torch.dtype] = None, inner=()) -> int:
+    def routed_tile_rows(self, n_tokens: int = 0, dtype: Optional[torch.dtype] = None, inner=(), per_expert: float = 0.0) -> int:
         """Rows of a tile of the per-expert products: the tensor-core kernel's in bfloat16 when every product's inner
-        size (`inner`) is a multiple of 8, else the CUDA-core kernel's."""
+        size (`inner`) is a multiple of 8 (64, or 128 when an expert gets about that many rows: `per_expert`), else the
+        CUDA-core kernel's."""
         if dtype == torch.bfloat16 and self.tensor_cores and self.routed_tensor_cores and inner and all(k % 8 == 0 for k in inner):
-            return int(self.lib("tensorcore").llm_routed_product_mma_rows())
+            return int(self.lib("tensorcore").llm_routed_product_mma_rows(c_int(int(per_expert))))
         return int(self.lib().llm_routed_product_rows())
 
     def routed_group(self, idx: torch.Tensor, experts: int, tile: int, ws, tag: str):
@@ -977,11 +978,11 @@ class CudaOps:
         if epilogue == "share":
             _need(share, "routed_product.share", torch.float32)
         if a.dtype == torch.bfloat16 and self.tensor_cores and tile_rows.shape[1] != self.routed_tile_rows():
-            lib = self.lib("tensorcore")  # tiles made for the tensor-core kernel
-            assert tile_rows.shape[1] == int(lib.llm_routed_product_mma_rows())
+            lib = self.lib("tensorcore")  # tiles made for the tensor-core kernel (64 or 128 rows)
             assert out.dtype == (torch.bfloat16 if epilogue == "gelu" else torch.float32)
             self._check(lib.llm_routed_product_mma(_ptr(a), c_longlong(a.stride(0)), c_int(a_div), _ptr(w), c_int(N), c_int(K),
-                                                   _ptr(tile_expert), _ptr(tile_rows), c_int(tile_expert.numel()), _ptr(out),
+                                                   _ptr(tile_expert), _ptr(tile_rows), c_int(tile_expert.numel()),
+                                                   c_int(tile_rows.shape[1]), _ptr(out),
                                                    c_longlong(out.stride(0)), c_int({"gelu": 0, "share": 1}[epilogue]), _ptr(share),
                                                    _stream()), lib)
             return out

@@ -40,6 +40,13 @@ class RoutedMLP(FeedForward):
             out += [TensorNeed(up, (spec.intermediate, spec.hidden)), TensorNeed(down, (spec.hidden, spec.intermediate))]
         return out
 
+    def kernel_notes(self):
+        s = self.spec
+        if self.env.dtype == torch.bfloat16 and (s.hidden % 8 or s.intermediate % 8):
+            return [f"routed feed-forward: sizes {s.hidden} and {s.intermediate} are not both multiples of 8: the per-expert "
+                    "products run on CUDA cores"]
+        return []
+
     def load(self, tensors) -> None:
         s = self.spec
         self.router = tensors[s.router_weight]
@@ -55,7 +62,7 @@ class RoutedMLP(FeedForward):
         idx = ctx.ws.get("routed.idx", (n, s.top), torch.int32)
         share = ctx.ws.get("routed.share", (n, s.top), torch.float32)
         ops.route(x, self.router, self.bias, s.top, idx, share)
-        tile = ops.routed_tile_rows(n, dt, (s.hidden, s.intermediate))
+        tile = ops.routed_tile_rows(n, dt, (s.hidden, s.intermediate), n * s.top / s.experts)
         tile_expert, tile_rows = ops.routed_group(idx, s.experts, tile, ctx.ws, "routed")
         act = ctx.ws.get("routed.act", (n * s.top, s.intermediate), dt)
         ops.routed_product(x, s.top, self.w_up, tile_expert, tile_rows, act, "gelu")

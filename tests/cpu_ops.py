@@ -174,7 +174,7 @@ class CpuOps:
         idx.copy_(order.to(torch.int32))
         share.copy_(torch.softmax(torch.gather(z, 1, order), dim=-1))
 
-    def routed_tile_rows(self, n_tokens=0, dtype=None, inner=()):
+    def routed_tile_rows(self, n_tokens=0, dtype=None, inner=(), per_expert=0.0):
         return 4
 
     def routed_group(self, idx, experts, tile, ws, tag):

@@ -54,7 +54,7 @@ def test_latent_attention_tensor_cores_and_cuda_cores(H, R, dr, page, window):
     assert ops.latent_attention_kernel(H, R, dr, page) == "tensor cores"
 
 
-@pytest.mark.parametrize("E,N,K,pairs_per_token,n", [(5, 72, 40, 2, 37), (16, 200, 128, 4, 300), (3, 64, 264, 1, 5)])
+@pytest.mark.parametrize("E,N,K,pairs_per_token,n", [(5, 72, 40, 2, 37), (16, 200, 128, 4, 300), (3, 64, 264, 1, 5), (4, 328, 200, 2, 700)])
 def test_routed_products_tensor_cores_against_cuda_cores_and_formula(E, N, K, pairs_per_token, n):
     ops = get_ops()
     from llmengine.engine.context import Workspace
@@ -66,7 +66,8 @@ def test_routed_products_tensor_cores_against_cuda_cores_and_formula(E, N, K, pa
     share = torch.rand(n * pairs_per_token, generator=g).to(DEV)
     full = torch.einsum("tk,enk->ten", x.double().cpu(), w.double().cpu())  # every expert for every token
     picked = torch.stack([full[t, idx[t, j].item()] for t in range(n) for j in range(pairs_per_token)])
-    for tile in (ops.routed_tile_rows(n, torch.bfloat16, (K,)), ops.routed_tile_rows(n, torch.float32)):
+    # tiles of the tensor-core kernel (128 rows where an expert gets many, else 64) and of the CUDA-core kernel
+    for tile in (ops.routed_tile_rows(n, torch.bfloat16, (K,), n * pairs_per_token / E), ops.routed_tile_rows(n, torch.float32)):
         te, tr = ops.routed_group(idx, E, tile, ws, f"t{tile}")
         seen = sorted(p for p in tr.cpu().reshape(-1).tolist() if p >= 0)
         assert seen == list(range(n * pairs_per_token)), "every pair lies in exactly one tile"
