@@ -566,7 +566,7 @@ def main():
                     help="decode: the contract's line (default). serve / long: the workloads of the 3B and 8B configurations, a line of their own")
     ap.add_argument("--budget", type=int, default=2048, help="serve: prompt tokens a step (max_prefill_tokens_per_step)")
     ap.add_argument("--design", choices=["vapelix"], default=None,
-                    help="instead of the contract's line: prompt and decode throughput of this design at a few layer sizes, "
+                    help="instead of the default line: prompt and decode throughput of this design at a few layer sizes, "
                          "beside the Llama decoder of equal size (one JSON line a size)")
     ap.add_argument("--sizes", default="", help="--design: comma list of " + ",".join(sorted(DESIGN_SIZES)) + " (default: all)")
     ap.add_argument("--reference-setup-limit", type=float, default=900.0, help="seconds the reference arm may spend filling contexts")

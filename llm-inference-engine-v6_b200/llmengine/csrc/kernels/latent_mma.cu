@@ -35,7 +35,9 @@ struct LatentParams {
   float* part_o; float* part_ml; int split_keys, n_splits; long long n_tokens;
 };
 
-// DT: accumulator tiles of 16 columns a warp; R = 64 * DT. RGS: groups of 16 rows a CTA. 2: 32 rows, key tiles of 64,
+// DT: accumulator tiles of 16 columns a warp; R = 64 * DT. RGS: groups of 16 rows a CTA. 1: 16 rows, four warps (single
+// tokens of up to 16 heads cut into splits; with splits of one key tile the CTA keeps one key buffer, 98 KB at 576
+// numbers a row, and two CTAs share an SM). 2: 32 rows, key tiles of 64,
 // eight warps (steps of single tokens and short portions, and rows whose length is no multiple of 32). 4: 64 rows, key
 // tiles of 32, sixteen warps: the same shared memory holds twice the rows, so a fetched key row serves twice as many
 // queries and twice the warps hide one another's waits (prompt portions).
@@ -46,7 +48,8 @@ __global__ void __launch_bounds__(RGS * 128) latent_attention_mma_kernel(const L
   const int Dk = p.Dk, LD = Dk + 8, CH = Dk / 8;  // padded row; 16-byte chunks of a row
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);            // [LM_ROWS][LD]
   bf16* k_s = q_s + LM_ROWS * LD;                           // [2][LM_KEYS][LD]
-  float* s_s = reinterpret_cast<float*>(k_s + 2 * LM_KEYS * LD);  // [LM_ROWS][LM_SLD]
+  const int buffers = (SPLIT && p.split_keys == LM_KEYS) ? 1 : 2;  // a split of one tile needs one buffer
+  float* s_s = reinterpret_cast<float*>(k_s + buffers * LM_KEYS * LD);  // [LM_ROWS][LM_SLD]
 
   dep_launch();
   dep_wait();
@@ -78,28 +81,44 @@ __global__ void __launch_bounds__(RGS * 128) latent_attention_mma_kernel(const L
   for (int r = warp; r < LM_ROWS; r += LM_THREADS / 32) {
     const bool valid = row_valid(r);
     const bf16* src = valid ? p.ql + ((size_t)(tok_base + r / gh) * p.H + head0 + r % gh) * Dk : p.ql;
-    for (int ch = lane; ch < CH; ch += 32)
-      *reinterpret_cast<uint4*>(q_s + r * LD + ch * 8) = valid ? *reinterpret_cast<const uint4*>(src + ch * 8) : make_uint4(0, 0, 0, 0);
+    // asynchronous copies (zeros for padding rows): all of a CTA's query rows are on their way at once, in the same
+    // group as the first key tile
+    for (int ch = lane; ch < CH; ch += 32) cp_async16(q_s + r * LD + ch * 8, src + (valid ? ch * 8 : 0), valid);
   }
 
-  auto load_tile = [&](int kt, int buf) {
-    bf16* kd = k_s + (size_t)buf * LM_KEYS * LD;
-    for (int r = warp; r < LM_KEYS; r += LM_THREADS / 32) {
-      const int key = kt * LM_KEYS + r;
-      const bool valid = key >= lo && key <= hi;
-      const bf16* src = p.cache;
-      if (valid) {
+  // A warp copies the tile's rows warp, warp + NW, ...; lane i first looks up where row i lies (one round of
+  // block-table reads a tile, asked for one tile ahead of the copies that use them), then the copies follow.
+  constexpr int NW = LM_THREADS / 32, RPW = LM_KEYS / NW;  // warps; rows of a tile a warp copies
+  auto lookup = [&](int kt) -> long long {
+    long long off = -1;  // -1: the row lies outside the keys this CTA reads (zeros are written instead)
+    if (lane < RPW) {
+      const int key = kt * LM_KEYS + warp + lane * NW;
+      if (key >= lo && key <= hi) {
         const int pg = key / p.page_size;
-        src += ((size_t)table[pg] * p.page_size + (size_t)(key - pg * p.page_size)) * Dk;
+        off = ((long long)table[pg] * p.page_size + (key - pg * p.page_size)) * Dk;
       }
-      bf16* dst = kd + r * LD;
+    }
+    return off;
+  };
+  auto load_tile = [&](int buf, long long my_off) {
+    bf16* kd = k_s + (size_t)buf * LM_KEYS * LD;
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) {
+      const long long off = __shfl_sync(0xffffffffu, my_off, i);
+      const bool valid = off >= 0;
+      bf16* dst = kd + (warp + i * NW) * LD;
+      const bf16* src = p.cache + (valid ? off : 0);
       for (int ch = lane; ch < CH; ch += 32) cp_async16(dst + ch * 8, src + (valid ? ch * 8 : 0), valid);
     }
   };
 
   const int kt_first = lo / LM_KEYS, kt_last = hi / LM_KEYS;
   const bool any = hi >= lo;
-  if (any) load_tile(kt_first, 0);
+  long long next_off = -1;
+  if (any) {
+    load_tile(0, lookup(kt_first));
+    if (kt_first < kt_last) next_off = lookup(kt_first + 1);
+  }
   cp_async_commit();
 
   const int row_a = rg * 16 + lane / 4, row_b = row_a + 8;  // the two rows this thread holds
@@ -116,7 +135,10 @@ __global__ void __launch_bounds__(RGS * 128) latent_attention_mma_kernel(const L
   if (any) {
     for (int kt = kt_first; kt <= kt_last; ++kt) {
       const int buf = (kt - kt_first) & 1;
-      if (kt < kt_last) load_tile(kt + 1, buf ^ 1);
+      if (kt < kt_last) {
+        load_tile(buf ^ 1, next_off);
+        if (kt + 1 < kt_last) next_off = lookup(kt + 2);  // used an iteration from now
+      }
       cp_async_commit();
       cp_async_wait<1>();
       __syncthreads();  // tile kt (and, the first time, the query rows) visible
@@ -258,10 +280,8 @@ __global__ void __launch_bounds__(RGS * 128) latent_attention_mma_kernel(const L
       const size_t slot = ((size_t)split * p.n_tokens + tok) * p.H + head;
       float* dst = p.part_o + slot * p.R + col0;
 #pragma unroll
-      for (int d = 0; d < 2 * DT; ++d) {
-        dst[d * 8] = o_acc[d][2 * half] * inv;
-        dst[d * 8 + 1] = o_acc[d][2 * half + 1] * inv;
-      }
+      for (int d = 0; d < 2 * DT; ++d)
+        *reinterpret_cast<float2*>(dst + d * 8) = make_float2(o_acc[d][2 * half] * inv, o_acc[d][2 * half + 1] * inv);
       if (cw == 0 && (lane % 4) == 0) {
         p.part_ml[slot * 2] = half ? m_b : m_a;  // log2 units; -inf when this split saw no key of the row
         p.part_ml[slot * 2 + 1] = half ? l_b : l_a;
@@ -272,7 +292,7 @@ __global__ void __launch_bounds__(RGS * 128) latent_attention_mma_kernel(const L
 
 // Merges the splits of every (token, head) in index order: out = sum_s w_s o_s / sum_s w_s, w_s = l_s * 2^(m_s - max m).
 // One block per (token, head): the weights are computed once into shared memory, then every thread owns columns.
-constexpr int LC_THREADS = 128, LC_MAX_SPLITS = 128;
+constexpr int LC_THREADS = 256, LC_MAX_SPLITS = 128;
 __global__ void __launch_bounds__(LC_THREADS)
     latent_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int n_splits, long long n_tokens, int H,
                           int R, bf16* __restrict__ out) {
@@ -292,7 +312,9 @@ __global__ void __launch_bounds__(LC_THREADS)
   float mx = warp_max(m);
   if ((tid & 31) == 0) red[tid >> 5] = mx;
   __syncthreads();
-  mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+  mx = red[0];
+#pragma unroll
+  for (int i = 1; i < LC_THREADS / 32; ++i) mx = fmaxf(mx, red[i]);
   if (tid < LC_MAX_SPLITS) w_s[tid] = (tid < n_splits && m != -INFINITY) ? l * exp2f(m - mx) : 0.f;
   __syncthreads();
   float den = 0.f;
@@ -312,13 +334,14 @@ __global__ void __launch_bounds__(LC_THREADS)
   }
 }
 
-size_t latent_smem(int Dk, int rgs = 2) {
-  return (size_t)(lm_rows(rgs) + 2 * lm_keys(rgs)) * (Dk + 8) * sizeof(bf16) + (size_t)lm_rows(rgs) * (lm_keys(rgs) + 4) * sizeof(float);
+// buffers: 2, or 1 for CTAs that read a single key tile (splits of 64 keys): the second buffer is never touched then
+size_t latent_smem(int Dk, int rgs = 2, int buffers = 2) {
+  return (size_t)(lm_rows(rgs) + buffers * lm_keys(rgs)) * (Dk + 8) * sizeof(bf16) + (size_t)lm_rows(rgs) * (lm_keys(rgs) + 4) * sizeof(float);
 }
 
 template <int DT, bool SPLIT, int RGS>
 int launch_latent_as(const LatentParams& p, dim3 grid, cudaStream_t stream) {
-  const size_t smem = latent_smem(p.Dk, RGS);
+  const size_t smem = latent_smem(p.Dk, RGS, (SPLIT && p.split_keys == lm_keys(RGS)) ? 1 : 2);
   if (smem > 48 * 1024 && cudaFuncSetAttribute(latent_attention_mma_kernel<DT, SPLIT, RGS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return 1;
   launch_kernel(latent_attention_mma_kernel<DT, SPLIT, RGS>, grid, RGS * 128, smem, stream, p);
@@ -327,7 +350,8 @@ int launch_latent_as(const LatentParams& p, dim3 grid, cudaStream_t stream) {
 
 template <int DT>
 int launch_latent(const LatentParams& p, dim3 grid, bool split, bool wide, cudaStream_t stream) {
-  if (split) return launch_latent_as<DT, true, 2>(p, grid, stream);
+  // single tokens: 16 rows a CTA where the heads fit them (a smaller footprint: two CTAs an SM), else 32
+  if (split) return p.gh <= 16 ? launch_latent_as<DT, true, 1>(p, grid, stream) : launch_latent_as<DT, true, 2>(p, grid, stream);
   return wide ? launch_latent_as<DT, false, 4>(p, grid, stream) : launch_latent_as<DT, false, 2>(p, grid, stream);
 }
 
@@ -363,7 +387,7 @@ extern "C" int llm_latent_attention_mma(const void* ql, const void* cache, const
   // the wide form (64 rows a CTA) for steps with portions of at least 64 rows, where rows are a multiple of 32 numbers
   const bool split = n_splits > 1;
   const bool wide = !split && (long long)max_new_tokens * H >= 64 && (R + dr) % 32 == 0 && latent_smem(R + dr, 4) <= 220 * 1024;
-  const int rows = lm_rows(wide ? 4 : 2);
+  const int rows = lm_rows(wide ? 4 : (split && H <= 16 ? 1 : 2));
   p.block_table = block_table; p.max_blocks = max_blocks; p.H = H; p.gh = H < rows ? H : rows;
   p.n_htiles = (H + p.gh - 1) / p.gh; p.R = R; p.Dk = R + dr; p.page_size = page_size; p.window = window; p.scale = scale;
   p.out = (bf16*)out; p.n_splits = n_splits; p.split_keys = split_keys; p.n_tokens = n_tokens;

@@ -113,6 +113,93 @@ __global__ void __launch_bounds__(RM_THREADS * WM)
   }
 }
 
+
+// Few rows an expert (steps of single tokens): a tile of 16 rows x 64 columns, the four warps side by side along the
+// columns, and a ring of six stages: the expert's matrix is all that moves, and what bounds the kernel is how many of
+// its bytes are on their way to an SM at a time (a stage holds 9 KB of it and 2 KB of rows).
+constexpr int RS_ROWS = 16, RS_STAGES = 6;
+constexpr size_t RS_SMEM = (size_t)RS_STAGES * (RS_ROWS + RM_COLS) * RM_LD * sizeof(bf16);
+
+template <typename TO, int EPI>
+__global__ void __launch_bounds__(RM_THREADS)
+    routed_product_mma_few_kernel(const bf16* __restrict__ a, long long lda, int a_div, const bf16* __restrict__ w, long long w_stride, int N,
+                                  int K, const int* __restrict__ tile_expert, const int* __restrict__ tile_rows, TO* __restrict__ out,
+                                  long long ldo, const float* __restrict__ share) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  bf16 (*a_s)[RS_ROWS][RM_LD] = reinterpret_cast<bf16 (*)[RS_ROWS][RM_LD]>(smem_raw);
+  bf16 (*w_s)[RM_COLS][RM_LD] = reinterpret_cast<bf16 (*)[RM_COLS][RM_LD]>(smem_raw + (size_t)RS_STAGES * RS_ROWS * RM_LD * sizeof(bf16));
+  __shared__ int rows_s[RS_ROWS];
+  dep_launch();
+  dep_wait();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int e = tile_expert[blockIdx.y];
+  if (e < 0) return;
+  const int n0 = blockIdx.x * RM_COLS;
+  if (tid < RS_ROWS) rows_s[tid] = tile_rows[(size_t)blockIdx.y * RS_ROWS + tid];
+  __syncthreads();
+  const bf16* we = w + (size_t)e * w_stride;
+
+  auto load = [&](int kt, int buf) {
+    {  // rows: 16 x 8 chunks, one a thread
+      const int r = tid / (RM_BK / 8), ch = tid % (RM_BK / 8);
+      const int k = kt * RM_BK + ch * 8;
+      const int pair = rows_s[r];
+      const bool va = pair >= 0 && k < K;
+      cp_async16(&a_s[buf][r][ch * 8], a + (va ? (size_t)(pair / a_div) * lda + k : 0), va);
+    }
+#pragma unroll
+    for (int i = 0; i < RM_COLS * (RM_BK / 8) / RM_THREADS; ++i) {
+      const int c = tid + i * RM_THREADS, r = c / (RM_BK / 8), ch = c % (RM_BK / 8);
+      const int k = kt * RM_BK + ch * 8;
+      const bool vw = n0 + r < N && k < K;
+      cp_async16(&w_s[buf][r][ch * 8], we + (vw ? (size_t)(n0 + r) * K + k : 0), vw);
+    }
+  };
+
+  float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+  const int k_tiles = (K + RM_BK - 1) / RM_BK;
+#pragma unroll
+  for (int st = 0; st < RS_STAGES - 1; ++st) {
+    if (st < k_tiles) load(st, st);
+    cp_async_commit();
+  }
+  for (int kt = 0; kt < k_tiles; ++kt) {
+    const int buf = kt % RS_STAGES;
+    cp_async_wait<RS_STAGES - 2>();
+    __syncthreads();
+    if (kt + RS_STAGES - 1 < k_tiles) load(kt + RS_STAGES - 1, (kt + RS_STAGES - 1) % RS_STAGES);
+    cp_async_commit();
+#pragma unroll
+    for (int ks = 0; ks < RM_BK / 16; ++ks) {
+      uint32_t af[4], b[4];
+      ldmatrix_x4(af, &a_s[buf][lane % 16][ks * 16 + (lane / 16) * 8]);
+      ldmatrix_x4(b, &w_s[buf][warp * 16 + (lane % 8) + (lane / 16) * 8][ks * 16 + ((lane / 8) % 2) * 8]);
+      mma_bf16(acc[0], af, b[0], b[1]);
+      mma_bf16(acc[1], af, b[2], b[3]);
+    }
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int pair = rows_s[lane / 4 + half * 8];
+    if (pair < 0) continue;
+    const float sc = EPI == 1 ? share[pair] : 1.0f;
+    TO* dst = out + (size_t)pair * ldo;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+      for (int el = 0; el < 2; ++el) {
+        const int n = n0 + warp * 16 + j * 8 + 2 * (lane % 4) + el;
+        if (n >= N) continue;
+        float v = acc[j][2 * half + el];
+        if (EPI == 0) v = 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
+        else v *= sc;
+        dst[n] = from_f32<TO>(v);
+      }
+    }
+  }
+}
+
 // The same main loop for a product per head over ALL tokens: out[t, h, :] = w[h] a[t, h, :] (a rows lda apart, a head's
 // columns lda_h apart; out likewise), optionally times sigmoid of a gate given as float32 partial sums
 // [parts, tokens, gwidth] at columns g_off + h * N + n. grid (N / 64, tokens / 64, heads).
@@ -197,8 +284,10 @@ __global__ void __launch_bounds__(RM_THREADS)
 
 }  // namespace
 
-// Rows of a tile: 64, or 128 when an expert gets about that many rows or more.
-extern "C" int llm_routed_product_mma_rows(int rows_per_expert) { return rows_per_expert >= 96 ? 2 * RM_ROWS : RM_ROWS; }
+// Rows of a tile: 64; 128 when an expert gets about that many rows or more; 16 when it gets a few.
+extern "C" int llm_routed_product_mma_rows(int rows_per_expert) {
+  return rows_per_expert >= 96 ? 2 * RM_ROWS : (rows_per_expert <= 8 ? RS_ROWS : RM_ROWS);
+}
 
 // Whether the tensor-core kernel takes these operands: 16-byte aligned rows of K % 8 == 0.
 extern "C" int llm_routed_product_mma_supported(const void* a, long long lda, const void* w, int K) {
@@ -226,8 +315,27 @@ extern "C" int llm_routed_product_mma(const void* a, long long lda, int a_div, c
   if (max_tiles == 0) return LLM_OK;
   LLM_REQUIRE(llm_routed_product_mma_supported(a, lda, w, K), "routed_product_mma: operands must be 16-byte aligned with K and the row stride multiples of 8");
   LLM_REQUIRE(N > 0 && a_div > 0 && max_tiles > 0 && max_tiles <= 65535, "routed_product_mma: bad sizes");
-  LLM_REQUIRE(tile == RM_ROWS || tile == 2 * RM_ROWS, "routed_product_mma: tiles of %d rows (64 or 128)", tile);
+  LLM_REQUIRE(tile == RS_ROWS || tile == RM_ROWS || tile == 2 * RM_ROWS, "routed_product_mma: tiles of %d rows (16, 64 or 128)", tile);
   LLM_REQUIRE(epilogue == 0 || (epilogue == 1 && share), "routed_product_mma: unknown epilogue %d", epilogue);
+  if (tile == RS_ROWS) {
+    static bool raised_few = false;
+    if (!raised_few) {
+      LLM_REQUIRE(cudaFuncSetAttribute(routed_product_mma_few_kernel<bf16, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RS_SMEM) == cudaSuccess &&
+                  cudaFuncSetAttribute(routed_product_mma_few_kernel<float, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RS_SMEM) == cudaSuccess,
+                  "routed_product_mma: cannot raise the shared memory limit");
+      raised_few = true;
+    }
+    dim3 grid_few(ceil_div(N, RM_COLS), max_tiles);
+    const long long wsf = (long long)N * K;
+    if (epilogue == 0)
+      launch_kernel(routed_product_mma_few_kernel<bf16, 0>, grid_few, RM_THREADS, RS_SMEM, stream, (const bf16*)a, lda, a_div, (const bf16*)w, wsf,
+                    N, K, tile_expert, tile_rows, (bf16*)out, ldo, share);
+    else
+      launch_kernel(routed_product_mma_few_kernel<float, 1>, grid_few, RM_THREADS, RS_SMEM, stream, (const bf16*)a, lda, a_div, (const bf16*)w, wsf,
+                    N, K, tile_expert, tile_rows, (float*)out, ldo, share);
+    LLM_CHECK_LAUNCH("routed_product_mma");
+    return LLM_OK;
+  }
   const int wm = tile / RM_ROWS;
   dim3 grid(ceil_div(N, RM_COLS * wm), max_tiles);
   const long long ws = (long long)N * K;

@@ -900,7 +900,7 @@ class CudaOps:
         return out
 
     LATENT_TARGET_CTAS = 296  # two CTAs of the latent attention kernel on each of the 148 SMs
-    LATENT_MIN_SPLIT_KEYS = 128
+    LATENT_MIN_SPLIT_KEYS = 64
 
     def _latent_split_policy(self, ctas: int, max_seq_len: int):
         """-> (number of key splits, keys per split) of a step of single tokens whose latent attention would run as
