@@ -14,7 +14,7 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ out, float* __restrict__ sumsq, int dim, int vocab,
-                             const float* __restrict__ next_w, bf16* __restrict__ scaled, long long ld_scaled) {
+                             const float* __restrict__ next_w, bf16* __restrict__ scaled, long long ld_scaled, float scale) {
   __shared__ float red[33];
   dep_launch();
   dep_wait();
@@ -25,7 +25,7 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
   float* dst = out + (size_t)row * dim;
   float ss = 0.f;
   for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-    const float v = to_f32(src[i]);
+    const float v = to_f32(src[i]) * scale;  // scale 1 leaves the row as it is
     dst[i] = v;
     ss += v * v;
     if (scaled) scaled[(size_t)row * ld_scaled + i] = __float2bfloat16_rn(v * next_w[i]);
@@ -39,15 +39,15 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 // next_w, scaled (both or neither): scaled [rows, ld_scaled] bf16 = next_w * row, the operand of the
 // product behind a norm with weight next_w whose 1/rms the product's consumer applies from sumsq.
 extern "C" int llm_embed(const void* table, int table_dtype, const int* ids, float* out, float* sumsq, int n_rows,
-                         int dim, int vocab, const float* next_w, void* scaled, long long ld_scaled, cudaStream_t stream) {
+                         int dim, int vocab, const float* next_w, void* scaled, long long ld_scaled, float scale, cudaStream_t stream) {
   if (n_rows == 0) return LLM_OK;
   LLM_REQUIRE((next_w == nullptr) == (scaled == nullptr), "embed: the scaled copy needs the weight it is scaled with");
   LLM_REQUIRE(n_rows > 0 && dim > 0 && vocab > 0, "embed: bad sizes rows=%d dim=%d vocab=%d", n_rows, dim, vocab);
   const int threads = dim >= 1024 ? 256 : 128;
   if (table_dtype == LLM_F32)
-    launch_kernel(embed_kernel<float>, n_rows, threads, 0, stream, (const float*)table, ids, out, sumsq, dim, vocab, next_w, (bf16*)scaled, ld_scaled);
+    launch_kernel(embed_kernel<float>, n_rows, threads, 0, stream, (const float*)table, ids, out, sumsq, dim, vocab, next_w, (bf16*)scaled, ld_scaled, scale);
   else if (table_dtype == LLM_BF16)
-    launch_kernel(embed_kernel<bf16>, n_rows, threads, 0, stream, (const bf16*)table, ids, out, sumsq, dim, vocab, next_w, (bf16*)scaled, ld_scaled);
+    launch_kernel(embed_kernel<bf16>, n_rows, threads, 0, stream, (const bf16*)table, ids, out, sumsq, dim, vocab, next_w, (bf16*)scaled, ld_scaled, scale);
   else
     LLM_REQUIRE(false, "embed: unknown table dtype %d", table_dtype);
   LLM_CHECK_LAUNCH("embed");
@@ -446,5 +446,62 @@ extern "C" int llm_stream_add(float* h, const float* a, int na, long long sa, co
   else
     LLM_REQUIRE(false, "stream_add: unknown dtype %d", copy_dtype);
   LLM_CHECK_LAUNCH("stream_add");
+  return LLM_OK;
+}
+
+// ------------------------------------------------------------------------------------ norm of a sub-layer's output
+// A block whose norms sit on the sub-layers' OUTPUTS: y = a (+ b), float32 [n, dim] or partial sums [parts, n, dim] added in
+// index order; h[r] += ((y / sqrt(mean(y^2) + eps)) * w) * ls  (ls: an optional per-column layer scale); copy[r] (optional) =
+// the new h[r] in the engine dtype, the operand of the products that read the stream next. One block a row, float32.
+namespace {
+template <typename T>
+__global__ void norm_add_kernel(float* __restrict__ h, const float* __restrict__ a, int na, size_t sa, const float* __restrict__ b, int nb,
+                                size_t sb, const float* __restrict__ w, const float* __restrict__ ls, float eps, T* __restrict__ copy, int dim) {
+  __shared__ float red[33];
+  dep_launch();
+  dep_wait();
+  const size_t base = (size_t)blockIdx.x * dim;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    float y = a[base + i];
+    for (int p = 1; p < na; ++p) y += a[(size_t)p * sa + base + i];
+    if (b) {
+      float d = b[base + i];
+      for (int p = 1; p < nb; ++p) d += b[(size_t)p * sb + base + i];
+      y += d;
+    }
+    ss += y * y;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    float y = a[base + i];
+    for (int p = 1; p < na; ++p) y += a[(size_t)p * sa + base + i];
+    if (b) {
+      float d = b[base + i];
+      for (int p = 1; p < nb; ++p) d += b[(size_t)p * sb + base + i];
+      y += d;
+    }
+    float v = y * inv * w[i];
+    if (ls) v *= ls[i];
+    const float x = h[base + i] + v;
+    h[base + i] = x;
+    if (copy) copy[base + i] = from_f32<T>(x);
+  }
+}
+}  // namespace
+
+extern "C" int llm_norm_add(float* h, const float* a, int na, long long sa, const float* b, int nb, long long sb, const float* w,
+                            const float* ls, float eps, void* copy, int copy_dtype, int n_rows, int dim, cudaStream_t stream) {
+  if (n_rows == 0) return LLM_OK;
+  LLM_REQUIRE(n_rows > 0 && dim > 0 && a != nullptr && na >= 1 && (b == nullptr || nb >= 1) && w != nullptr, "norm_add: bad arguments");
+  const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
+  if (copy_dtype == LLM_F32)
+    launch_kernel(norm_add_kernel<float>, n_rows, threads, 0, stream, h, a, na, (size_t)sa, b, nb, (size_t)sb, w, ls, eps, (float*)copy, dim);
+  else if (copy_dtype == LLM_BF16)
+    launch_kernel(norm_add_kernel<bf16>, n_rows, threads, 0, stream, h, a, na, (size_t)sa, b, nb, (size_t)sb, w, ls, eps, (bf16*)copy, dim);
+  else
+    LLM_REQUIRE(false, "norm_add: unknown dtype %d", copy_dtype);
+  LLM_CHECK_LAUNCH("norm_add");
   return LLM_OK;
 }

@@ -2,10 +2,12 @@
 //
 // CUDA-core matrix product with float32 accumulation: the true 32-bit path of the engine, and the
 // path that takes every shape (any M, N, K and row strides) in bfloat16 when the tensor-core
-// kernel refuses one. Each output element is one chain of fused multiply-adds over k = 0..K-1 in
-// ascending order, whatever M is and wherever the element lies in a tile, so a row's result does
-// not depend on what else is in the batch. This mirrors the serial dot of the reference's
-// matmul_f32 (src/kernels.cpp:33-57); no bias (src/engine.cpp:319-341).
+// kernel refuses one. Each output element is summed over k in ascending order, whatever M is and
+// wherever the element lies in a tile, so a row's result does not depend on what else is in the
+// batch: blocks of 16 k are chains of fused multiply-adds from zero, and the blocks' sums are added
+// with the rounding error of every addition carried along (two-sum) and added at the end, so that
+// the result is as exact as a sum of K / 16 terms allows and long inner sizes cost no accuracy.
+// The dot itself is the reference's matmul_f32 (src/kernels.cpp:33-57); no bias (src/engine.cpp:319-341).
 #include "common.cuh"
 
 namespace {
@@ -26,11 +28,11 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TA* __restrict__ a
   // loader mapping: 64 rows x 16 k; thread -> row tid/4, k offset (tid%4)*4 .. +3
   const int lr = tid >> 2, lk = (tid & 3) * 4;
 
-  float acc[TM][TN];
+  float acc[TM][TN], lost[TM][TN];  // the running sum and what its additions rounded away
 #pragma unroll
   for (int i = 0; i < TM; ++i)
 #pragma unroll
-    for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+    for (int j = 0; j < TN; ++j) acc[i][j] = lost[i][j] = 0.f;
 
   for (int k0 = 0; k0 < K; k0 += BK) {
     {
@@ -52,6 +54,11 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TA* __restrict__ a
       }
     }
     __syncthreads();
+    float blk[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) blk[i][j] = 0.f;
 #pragma unroll
     for (int kk = 0; kk < BK; ++kk) {
       float av[TM], wv[TN];
@@ -62,8 +69,18 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TA* __restrict__ a
 #pragma unroll
       for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+        for (int j = 0; j < TN; ++j) blk[i][j] = fmaf(av[i], wv[j], blk[i][j]);
     }
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) {
+        const float a0 = acc[i][j], b0 = blk[i][j];
+        const float sum = a0 + b0;
+        const float bv = sum - a0;
+        lost[i][j] += (a0 - (sum - bv)) + (b0 - bv);
+        acc[i][j] = sum;
+      }
     __syncthreads();
   }
 #pragma unroll
@@ -73,7 +90,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TA* __restrict__ a
 #pragma unroll
     for (int j = 0; j < TN; ++j) {
       const int n = n0 + tx * TN + j;
-      if (n < N) out[(size_t)m * ldo + n] = from_f32<TO>(acc[i][j]);
+      if (n < N) out[(size_t)m * ldo + n] = from_f32<TO>(acc[i][j] + lost[i][j]);
     }
   }
 }

@@ -77,6 +77,94 @@ __global__ void route_kernel(const T* __restrict__ x, long long ldx, const T* __
   if (lane < top) share[(size_t)tok * top + lane] /= denom;
 }
 
+// The router with scores over ALL experts and a limit on groups of experts:
+//   s = softmax(z) over the E experts;  choice = s + correction;  experts form n_groups equal groups of neighbours, a group's
+//   score is its largest choice score, and only experts of the `keep` best groups can be chosen (the others count as minus
+//   infinity); the `top` largest choice scores win (the lower index wins a tie); their weights are s (without the correction)
+//   divided by (their sum + norm_eps).
+template <typename T>
+__global__ void route_grouped_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ wr, const float* __restrict__ correction,
+                                     int D, int E, int top, int n_groups, int keep, float norm_eps, int* __restrict__ idx,
+                                     float* __restrict__ share) {
+  extern __shared__ float sh_r[];  // s[E], choice[E], group score[n_groups]
+  float* s = sh_r;
+  float* choice = sh_r + E;
+  float* gscore = sh_r + 2 * E;
+  dep_launch();
+  dep_wait();
+  const int tok = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const T* xr = x + (size_t)tok * ldx;
+  for (int e = warp; e < E; e += nw) {
+    const T* w = wr + (size_t)e * D;
+    float acc = 0.f;
+    for (int k = lane; k < D; k += 32) acc = fmaf(to_f32(xr[k]), to_f32(w[k]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) s[e] = acc;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float zmax = -INFINITY;
+  for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, s[e]);
+  zmax = warp_max(zmax);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) {
+    const float p = expf(s[e] - zmax);
+    s[e] = p;
+    sum += p;
+  }
+  sum = warp_sum(sum);
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) {
+    const float p = s[e] / sum;
+    s[e] = p;
+    choice[e] = p + (correction ? correction[e] : 0.f);
+  }
+  __syncwarp();
+  const int per = E / n_groups;
+  if (keep < n_groups) {
+    for (int g = lane; g < n_groups; g += 32) {
+      float best = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, choice[e]);
+      gscore[g] = best;
+    }
+    __syncwarp();
+    // a group stays if fewer than `keep` groups come before it (larger score, or the same score and a lower index)
+    for (int g = lane; g < n_groups; g += 32) {
+      const float mine = gscore[g];
+      int before = 0;
+      for (int o = 0; o < n_groups; ++o) before += (gscore[o] > mine || (gscore[o] == mine && o < g)) ? 1 : 0;
+      if (before >= keep)
+        for (int e = g * per; e < (g + 1) * per; ++e) choice[e] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  float total = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = choice[e];
+      if (v > best) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (bi == 0x7fffffff) bi = 0;  // fewer candidates than `top` (refused on the host; never read out of range)
+    const float p = s[bi];
+    total += p;
+    if (lane == 0) {
+      idx[(size_t)tok * top + k] = bi;
+      share[(size_t)tok * top + k] = p;
+      choice[bi] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  if (lane < top) share[(size_t)tok * top + lane] /= (total + norm_eps);
+}
+
 // One block. counts -> tiles per expert -> scatter. The order of an expert's rows depends on timing;
 // every row's result is computed on its own, so nothing depends on that order.
 __global__ void group_kernel(const int* __restrict__ idx, int n_pairs, int E, int tile, int max_tiles, int* __restrict__ tile_expert,
@@ -111,7 +199,8 @@ __global__ void group_kernel(const int* __restrict__ idx, int n_pairs, int E, in
 
 constexpr int RP_WARPS = 4, RP_ROWS = 8;  // rows of a tile of the CUDA-core product
 
-// epilogue 0: exact gelu; 1: times share[pair]
+// epilogue 0: exact gelu; 1: times share[pair]; 2: w holds 2 N rows, row 2 n a gate and row 2 n + 1 its up row:
+// out[p, n] = silu(gate) * up
 template <typename TA, typename TO>
 __global__ void __launch_bounds__(RP_WARPS * 32)
     routed_product_kernel(const TA* __restrict__ a, long long lda, int a_div, const TA* __restrict__ w, long long w_stride, int N, int K,
@@ -131,18 +220,36 @@ __global__ void __launch_bounds__(RP_WARPS * 32)
     pair[i] = rows[i];
     ar[i] = pair[i] >= 0 ? a + (size_t)(pair[i] / a_div) * lda : nullptr;
   }
-  const TA* wrow = w + (size_t)e * w_stride + (size_t)n * K;
-  float acc[RP_ROWS];
+  const TA* wrow = w + (size_t)e * w_stride + (size_t)(epilogue == 2 ? 2 * n : n) * K;
+  float acc[RP_ROWS], acc2[RP_ROWS];
 #pragma unroll
-  for (int i = 0; i < RP_ROWS; ++i) acc[i] = 0.f;
-  for (int k = lane; k < K; k += 32) {
-    const float wv = to_f32(wrow[k]);
+  for (int i = 0; i < RP_ROWS; ++i) acc[i] = acc2[i] = 0.f;
+  if (epilogue == 2) {
+    for (int k = lane; k < K; k += 32) {
+      const float wv = to_f32(wrow[k]), wu = to_f32(wrow[K + k]);
 #pragma unroll
-    for (int i = 0; i < RP_ROWS; ++i)
-      if (ar[i]) acc[i] = fmaf(to_f32(ar[i][k]), wv, acc[i]);
+      for (int i = 0; i < RP_ROWS; ++i)
+        if (ar[i]) {
+          const float av = to_f32(ar[i][k]);
+          acc[i] = fmaf(av, wv, acc[i]);
+          acc2[i] = fmaf(av, wu, acc2[i]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < RP_ROWS; ++i) {
+      const float g = warp_sum(acc[i]), u = warp_sum(acc2[i]);
+      acc[i] = g / (1.0f + expf(-g)) * u;
+    }
+  } else {
+    for (int k = lane; k < K; k += 32) {
+      const float wv = to_f32(wrow[k]);
+#pragma unroll
+      for (int i = 0; i < RP_ROWS; ++i)
+        if (ar[i]) acc[i] = fmaf(to_f32(ar[i][k]), wv, acc[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < RP_ROWS; ++i) acc[i] = warp_sum(acc[i]);
   }
-#pragma unroll
-  for (int i = 0; i < RP_ROWS; ++i) acc[i] = warp_sum(acc[i]);
   if (lane < RP_ROWS) {
     float v = 0.f;
     int p = -1;
@@ -151,7 +258,7 @@ __global__ void __launch_bounds__(RP_WARPS * 32)
       if (i == lane) { v = acc[i]; p = pair[i]; }
     if (p >= 0) {
       if (epilogue == 0) v = 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
-      else v *= share[p];
+      else if (epilogue == 1) v *= share[p];
       out[(size_t)p * ldo + n] = from_f32<TO>(v);
     }
   }
@@ -187,6 +294,26 @@ extern "C" int llm_route(const void* x, long long ldx, const void* wr, const flo
   return LLM_OK;
 }
 
+extern "C" int llm_route_grouped(const void* x, long long ldx, const void* wr, const float* correction, int n_tokens, int D, int E, int top,
+                                 int n_groups, int keep, float norm_eps, int* idx, float* share, int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(n_tokens > 0 && D > 0 && E > 0 && top > 0 && top <= E, "route: bad sizes experts=%d top=%d", E, top);
+  LLM_REQUIRE(top <= 32 && E <= 4096, "route: at most 32 of 4096 experts a token (got %d of %d)", top, E);
+  LLM_REQUIRE(n_groups >= 1 && keep >= 1 && keep <= n_groups && E % n_groups == 0, "route: %d experts do not form %d equal groups of which %d stay", E, n_groups, keep);
+  LLM_REQUIRE((long long)keep * (E / n_groups) >= top, "route: %d groups of %d experts cannot give %d choices", keep, E / n_groups, top);
+  const size_t smem = (size_t)(2 * E + n_groups) * sizeof(float);
+  if (dtype == LLM_F32)
+    launch_kernel(route_grouped_kernel<float>, n_tokens, 256, smem, stream, (const float*)x, ldx, (const float*)wr, correction, D, E, top, n_groups,
+                  keep, norm_eps, idx, share);
+  else if (dtype == LLM_BF16)
+    launch_kernel(route_grouped_kernel<bf16>, n_tokens, 256, smem, stream, (const bf16*)x, ldx, (const bf16*)wr, correction, D, E, top, n_groups,
+                  keep, norm_eps, idx, share);
+  else
+    LLM_REQUIRE(false, "route: unknown dtype %d", dtype);
+  LLM_CHECK_LAUNCH("route_grouped");
+  return LLM_OK;
+}
+
 extern "C" int llm_routed_tiles(int n_pairs, int E, int tile) { return (n_pairs + tile - 1) / tile + E; }
 
 extern "C" int llm_routed_group(const int* idx, int n_pairs, int E, int tile, int max_tiles, int* tile_expert, int* tile_rows,
@@ -206,9 +333,10 @@ extern "C" int llm_routed_product(const void* a, long long lda, int a_div, const
                                   int in_dtype, int out_dtype, cudaStream_t stream) {
   if (max_tiles == 0) return LLM_OK;
   LLM_REQUIRE(N > 0 && K > 0 && a_div > 0 && max_tiles > 0 && max_tiles <= 65535, "routed_product: bad sizes");
-  LLM_REQUIRE(epilogue == 0 || (epilogue == 1 && share), "routed_product: unknown epilogue %d", epilogue);
-  dim3 grid(ceil_div(N, RP_WARPS), max_tiles);
+  LLM_REQUIRE(epilogue == 0 || (epilogue == 1 && share) || (epilogue == 2 && N % 2 == 0), "routed_product: unknown epilogue %d", epilogue);
   const long long ws = (long long)N * K;
+  if (epilogue == 2) N /= 2;  // outputs: one for every (gate, up) pair of rows
+  dim3 grid(ceil_div(N, RP_WARPS), max_tiles);
 #define LLM_RP(TA, TO)                                                                                                         \
   launch_kernel(routed_product_kernel<TA, TO>, grid, RP_WARPS * 32, 0, stream, (const TA*)a, lda, a_div, (const TA*)w, ws, N, K, \
                 tile_expert, tile_rows, (TO*)out, ldo, epilogue, share)

@@ -5,7 +5,8 @@
 // pair / a_div of the operand), its B rows are 64 rows of the expert's matrix [N, K]. K is walked in blocks of 64
 // with cp.async through a ring of three stages in shared memory; four warps of 16 rows each (m16n8k16). Every output row is
 // written at its pair's own index; a row's sum depends on K alone, not on the rest of its tile.
-// Epilogue 0: the exact (erf) gelu, bfloat16 out; 1: times the pair's router weight, float32 out.
+// Epilogue 0: the exact (erf) gelu, bfloat16 out; 1: times the pair's router weight, float32 out; 2: the matrix holds a gate
+// row and its up row in turn (an even number of rows), out[p, n / 2] = silu(gate) * up, bfloat16 out.
 // heads_product_mma: the same tile loop for a product per head over all tokens (the key and value maps of latent attention).
 #include "common.cuh"
 #include "mma_common.cuh"
@@ -104,6 +105,13 @@ __global__ void __launch_bounds__(RM_THREADS * WM)
           const int n = n0 + warp_n * RM_COLS + j * 8 + 2 * (lane % 4) + el;
           if (n >= N) continue;
           float v = acc[i][j][2 * half + el];
+          if (EPI == 2) {  // the thread holds a gate column and, right of it, its up column
+            if (el == 0) {
+              const float u = acc[i][j][2 * half + 1];
+              dst[n / 2] = from_f32<TO>(v / (1.0f + expf(-v)) * u);
+            }
+            continue;
+          }
           if (EPI == 0) v = 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
           else v *= sc;
           dst[n] = from_f32<TO>(v);
@@ -192,6 +200,13 @@ __global__ void __launch_bounds__(RM_THREADS)
         const int n = n0 + warp * 16 + j * 8 + 2 * (lane % 4) + el;
         if (n >= N) continue;
         float v = acc[j][2 * half + el];
+        if (EPI == 2) {
+          if (el == 0) {
+            const float u = acc[j][2 * half + 1];
+            dst[n / 2] = from_f32<TO>(v / (1.0f + expf(-v)) * u);
+          }
+          continue;
+        }
         if (EPI == 0) v = 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
         else v *= sc;
         dst[n] = from_f32<TO>(v);
@@ -316,11 +331,12 @@ extern "C" int llm_routed_product_mma(const void* a, long long lda, int a_div, c
   LLM_REQUIRE(llm_routed_product_mma_supported(a, lda, w, K), "routed_product_mma: operands must be 16-byte aligned with K and the row stride multiples of 8");
   LLM_REQUIRE(N > 0 && a_div > 0 && max_tiles > 0 && max_tiles <= 65535, "routed_product_mma: bad sizes");
   LLM_REQUIRE(tile == RS_ROWS || tile == RM_ROWS || tile == 2 * RM_ROWS, "routed_product_mma: tiles of %d rows (16, 64 or 128)", tile);
-  LLM_REQUIRE(epilogue == 0 || (epilogue == 1 && share), "routed_product_mma: unknown epilogue %d", epilogue);
+  LLM_REQUIRE(epilogue == 0 || (epilogue == 1 && share) || (epilogue == 2 && N % 2 == 0), "routed_product_mma: unknown epilogue %d", epilogue);
   if (tile == RS_ROWS) {
     static bool raised_few = false;
     if (!raised_few) {
       LLM_REQUIRE(cudaFuncSetAttribute(routed_product_mma_few_kernel<bf16, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RS_SMEM) == cudaSuccess &&
+                  cudaFuncSetAttribute(routed_product_mma_few_kernel<bf16, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RS_SMEM) == cudaSuccess &&
                   cudaFuncSetAttribute(routed_product_mma_few_kernel<float, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RS_SMEM) == cudaSuccess,
                   "routed_product_mma: cannot raise the shared memory limit");
       raised_few = true;
@@ -329,6 +345,9 @@ extern "C" int llm_routed_product_mma(const void* a, long long lda, int a_div, c
     const long long wsf = (long long)N * K;
     if (epilogue == 0)
       launch_kernel(routed_product_mma_few_kernel<bf16, 0>, grid_few, RM_THREADS, RS_SMEM, stream, (const bf16*)a, lda, a_div, (const bf16*)w, wsf,
+                    N, K, tile_expert, tile_rows, (bf16*)out, ldo, share);
+    else if (epilogue == 2)
+      launch_kernel(routed_product_mma_few_kernel<bf16, 2>, grid_few, RM_THREADS, RS_SMEM, stream, (const bf16*)a, lda, a_div, (const bf16*)w, wsf,
                     N, K, tile_expert, tile_rows, (bf16*)out, ldo, share);
     else
       launch_kernel(routed_product_mma_few_kernel<float, 1>, grid_few, RM_THREADS, RS_SMEM, stream, (const bf16*)a, lda, a_div, (const bf16*)w, wsf,
@@ -343,6 +362,9 @@ extern "C" int llm_routed_product_mma(const void* a, long long lda, int a_div, c
   if (epilogue == 0)
     rc = wm == 2 ? launch_routed<bf16, 0, 2>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share)
                  : launch_routed<bf16, 0, 1>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share);
+  else if (epilogue == 2)
+    rc = wm == 2 ? launch_routed<bf16, 2, 2>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share)
+                 : launch_routed<bf16, 2, 1>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share);
   else
     rc = wm == 2 ? launch_routed<float, 1, 2>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share)
                  : launch_routed<float, 1, 1>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share);

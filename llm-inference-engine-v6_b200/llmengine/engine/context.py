@@ -79,6 +79,9 @@ class StepContext:
         self.stream_prescaled = None  # (rows times the first norm's weight, that weight), left by the embedding likewise
         self.next_norm = None  # the norm that reads the stream after the part being run has written it, if known
         self.norm_after_block = None  # the norm that reads the stream after the block being run
+        # what one layer of the step leaves for later layers of the same step, by a name they agree on (the values that a
+        # layer with value mixing hands to the layers after it); tensors of the workspace, so their addresses stay fixed
+        self.shared: Dict[str, object] = {}
 
 
 class StepBuffers:

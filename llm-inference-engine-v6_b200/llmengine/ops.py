@@ -80,6 +80,7 @@ class CudaOps:
         self.tma_decode_attention = True  # single decoded tokens: keys and values by TMA where the geometry allows it
         self.fused_decode_attention = True  # ... with the sum of the q|k|v parts, rotation and cache write in the same kernel
         self.latent_tensor_cores = True  # latent attention on mma.sync where the geometry allows it (off: CUDA cores)
+        self.gated_attention_tensor_cores = False  # gated attention on mma.sync where the geometry allows it (off: CUDA cores)
         self.routed_tensor_cores = True  # per-expert products of a routed feed-forward on mma.sync (off: CUDA cores)
         # Steps of few tokens: products that add their K pieces themselves, with the norm before, the residual sum
         # and SiLU * up folded in (gemm_few_tokens). Off: measured on B200 (batch 8, 2,048-token contexts, 1B layer
@@ -159,8 +160,8 @@ class CudaOps:
 
     # ------------------------------------------------------------------ elementwise
     def embed(self, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, sumsq: Optional[torch.Tensor] = None,
-              next_w: Optional[torch.Tensor] = None, scaled: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """out[n,:] (float32) = table[ids[n],:]; sumsq[n] (float32, optional) = sum of the row's squares;
+              next_w: Optional[torch.Tensor] = None, scaled: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
+        """out[n,:] (float32) = table[ids[n],:] * scale; sumsq[n] (float32, optional) = sum of the row's squares;
         scaled[n,:] (bfloat16, optional, with next_w float32 [dim]) = next_w * out[n,:]."""
         _need(table, "embed.table"); _need(ids, "embed.ids", torch.int32); _need(out, "embed.out", torch.float32)
         lib = self.lib()
@@ -176,7 +177,7 @@ class CudaOps:
             ld_scaled = scaled.stride(0)
         self._check(lib.llm_embed(_ptr(table), c_int(dtype_code(table.dtype)), _ptr(ids), _ptr(out), _ptr(sumsq), c_int(n),
                                   c_int(dim), c_int(table.shape[0]), _ptr(next_w if scaled is not None else None), _ptr(scaled),
-                                  c_longlong(ld_scaled), _stream()), lib)
+                                  c_longlong(ld_scaled), c_float(scale), _stream()), lib)
         return out
 
     def rmsnorm(self, h: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -947,6 +948,26 @@ class CudaOps:
         self._check(lib.llm_route(_ptr(x), c_longlong(x.stride(0)), _ptr(w), _ptr(bias), c_int(n), c_int(D), c_int(E), c_int(top),
                                   _ptr(idx), _ptr(share), c_int(dtype_code(x.dtype)), _stream()), lib)
 
+    ROUTED_EPILOGUES = {"gelu": 0, "share": 1, "silu_pairs": 2}
+
+    def route_grouped(self, x: torch.Tensor, w: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep: int,
+                      norm_eps: float, idx: torch.Tensor, share: torch.Tensor) -> None:
+        """Per token: s = softmax(w x) over all experts (float32); choice = s + correction; only experts of the `keep` of
+        `groups` equal groups of neighbours with the largest choice scores can be chosen; idx [n, top] = the largest choice
+        scores among them (the lower index wins a tie); share [n, top] = their s divided by (the sum of the chosen s + norm_eps)."""
+        _need(x, "route.x"); _need(w, "route.w", x.dtype); _need(idx, "route.idx", torch.int32); _need(share, "route.share", torch.float32)
+        n, D = x.shape
+        E = w.shape[0]
+        assert w.is_contiguous() and w.shape[1] == D and idx.is_contiguous() and share.is_contiguous()
+        assert idx.shape == (n, top) and share.shape == (n, top)
+        if correction is not None:
+            _need(correction, "route.correction", torch.float32)
+            assert correction.numel() == E
+        lib = self.lib()
+        self._check(lib.llm_route_grouped(_ptr(x), c_longlong(x.stride(0)), _ptr(w), _ptr(correction), c_int(n), c_int(D), c_int(E),
+                                          c_int(top), c_int(groups), c_int(keep), c_float(norm_eps), _ptr(idx), _ptr(share),
+                                          c_int(dtype_code(x.dtype)), _stream()), lib)
+
     def routed_tile_rows(self, n_tokens: int = 0, dtype: Optional[torch.dtype] = None, inner=(), per_expert: float = 0.0) -> int:
         """Rows of a tile of the per-expert products: the tensor-core kernel's in bfloat16 when every product's inner
         size (`inner`) is a multiple of 8 (64, or 128 when an expert gets about that many rows: `per_expert`), else the
@@ -971,26 +992,28 @@ class CudaOps:
     def routed_product(self, a: torch.Tensor, a_div: int, w: torch.Tensor, tile_expert: torch.Tensor, tile_rows: torch.Tensor,
                        out: torch.Tensor, epilogue: str, share: Optional[torch.Tensor] = None) -> torch.Tensor:
         """For every pair p of every tile (expert e): out[p, :] = epi(w[e] a[p // a_div, :]); w [E, N, K]. epilogue "gelu":
-        the exact (erf) gelu; "share": times share[p] (float32, flat)."""
+        the exact (erf) gelu; "share": times share[p] (float32, flat); "silu_pairs": w holds a gate row and its up row in turn
+        ([E, 2 F, K]) and out[p, f] = silu(gate_f) * up_f ([pairs, F])."""
         _need(a, "routed_product.a"); _need(w, "routed_product.w", a.dtype); _need(out, "routed_product.out")
         E, N, K = w.shape
-        assert w.is_contiguous() and a.shape[1] == K and out.shape[1] == N
+        assert w.is_contiguous() and a.shape[1] == K and out.shape[1] == (N // 2 if epilogue == "silu_pairs" else N)
+        assert epilogue != "silu_pairs" or N % 2 == 0
         if epilogue == "share":
             _need(share, "routed_product.share", torch.float32)
         if a.dtype == torch.bfloat16 and self.tensor_cores and tile_rows.shape[1] != self.routed_tile_rows():
             lib = self.lib("tensorcore")  # tiles made for the tensor-core kernel (64 or 128 rows)
-            assert out.dtype == (torch.bfloat16 if epilogue == "gelu" else torch.float32)
+            assert out.dtype == (torch.float32 if epilogue == "share" else torch.bfloat16)
             self._check(lib.llm_routed_product_mma(_ptr(a), c_longlong(a.stride(0)), c_int(a_div), _ptr(w), c_int(N), c_int(K),
                                                    _ptr(tile_expert), _ptr(tile_rows), c_int(tile_expert.numel()),
                                                    c_int(tile_rows.shape[1]), _ptr(out),
-                                                   c_longlong(out.stride(0)), c_int({"gelu": 0, "share": 1}[epilogue]), _ptr(share),
+                                                   c_longlong(out.stride(0)), c_int(self.ROUTED_EPILOGUES[epilogue]), _ptr(share),
                                                    _stream()), lib)
             return out
         assert tile_rows.shape[1] == self.routed_tile_rows()
         lib = self.lib()
         self._check(lib.llm_routed_product(_ptr(a), c_longlong(a.stride(0)), c_int(a_div), _ptr(w), c_int(N), c_int(K), _ptr(tile_expert),
                                            _ptr(tile_rows), c_int(tile_expert.numel()), _ptr(out), c_longlong(out.stride(0)),
-                                           c_int({"gelu": 0, "share": 1}[epilogue]), _ptr(share), c_int(dtype_code(a.dtype)),
+                                           c_int(self.ROUTED_EPILOGUES[epilogue]), _ptr(share), c_int(dtype_code(a.dtype)),
                                            c_int(dtype_code(out.dtype)), _stream()), lib)
         return out
 
@@ -1001,6 +1024,185 @@ class CudaOps:
         assert y.is_contiguous() and out.is_contiguous() and y.shape == (n * top, D)
         lib = self.lib()
         self._check(lib.llm_routed_combine(_ptr(y), _ptr(out), c_int(n), c_int(top), c_int(D), _stream()), lib)
+        return out
+
+    # ------------------------------------------------------------------ norms on a sub-layer's output
+    def norm_add(self, h: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor], weight: torch.Tensor, layer_scale: Optional[torch.Tensor],
+                 eps: float, copy: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> torch.Tensor:
+        """y = a (+ b): float32 [n, dim] or [parts, n, dim] partial sums added in index order; h[:n] += ((y / rms(y)) * weight) *
+        layer_scale (eps inside the root; layer_scale optional); copy[:n] (optional, float32 or bfloat16) = the new h."""
+        _need(h, "norm_add.h", torch.float32); _need(weight, "norm_add.weight", torch.float32)
+        n = h.shape[0] if n_rows is None else n_rows
+        dim = h.shape[-1]
+        args = []
+        for t, name in ((a, "a"), (b, "b")):
+            if t is None:
+                args += [c_void_p(0), c_int(0), c_longlong(0)]
+                continue
+            _need(t, "norm_add." + name, torch.float32)
+            assert t.is_contiguous() and t.shape[-1] == dim and t.shape[-2] == h.shape[0], "the sums must have the stream's shape"
+            args += [_ptr(t), c_int(t.shape[0] if t.dim() == 3 else 1), c_longlong(t.stride(0) if t.dim() == 3 else 0)]
+        if layer_scale is not None:
+            _need(layer_scale, "norm_add.layer_scale", torch.float32)
+            assert layer_scale.numel() == dim
+        code = F32
+        if copy is not None:
+            _need(copy, "norm_add.copy")
+            assert copy.is_contiguous() and copy.shape[-1] == dim and copy.shape[0] >= n
+            code = dtype_code(copy.dtype)
+        assert h.is_contiguous() and weight.numel() == dim and a is not None
+        lib = self.lib()
+        self._check(lib.llm_norm_add(_ptr(h), *args, _ptr(weight), _ptr(layer_scale), c_float(eps), _ptr(copy), c_int(code), c_int(n),
+                                     c_int(dim), _stream()), lib)
+        return h
+
+    # ------------------------------------------------------------------ gated attention
+    def qkv_prep(self, parts: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int, q_norm: Optional[torch.Tensor],
+                 k_norm: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], batch,
+                 block_table: torch.Tensor, q_out: torch.Tensor, kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor],
+                 mix_role: int = 0, mix_weight: Optional[torch.Tensor] = None, v_first: Optional[torch.Tensor] = None) -> None:
+        """From the float32 sums `parts` [p, n, width] of a product whose columns begin with [q: heads * dk | k: kv_heads * dk |
+        v: kv_heads * dv]: RMS norm of every query and key head with the weights q_norm / k_norm [dk] (None: no norm), rotation
+        of the first 2 * cos.shape[1] numbers of each head (half-split pairs) at the token's position, q into q_out
+        [n, heads * dk], k and v into the token's page of kcache [pages, kv_heads, page, dk] / vcache [.., dv] (None: no write).
+        mix_role 1: the values are also left in v_first (float32 [n, kv_heads * dv]); 2: v <- (1 - m) v + m v_first before
+        the write, m = mix_weight (a float32 scalar on the device)."""
+        _need(parts, "qkv_prep.parts", torch.float32); _need(q_out, "qkv_prep.q")
+        assert parts.dim() == 3 and parts.is_contiguous()
+        n = batch.n_tokens
+        rot_dims = 0 if cos is None else 2 * cos.shape[1]
+        for t, name in ((q_norm, "q_norm"), (k_norm, "k_norm"), (cos, "cos"), (sin, "sin"), (mix_weight, "mix_weight"), (v_first, "v_first")):
+            if t is not None:
+                _need(t, "qkv_prep." + name, torch.float32)
+                assert t.is_contiguous()
+        assert (q_norm is None or q_norm.numel() == dk) and (k_norm is None or k_norm.numel() == dk)
+        page = 1
+        if kcache is not None:
+            _need(kcache, "qkv_prep.kcache", q_out.dtype); _need(vcache, "qkv_prep.vcache", q_out.dtype)
+            assert kcache.is_contiguous() and vcache.is_contiguous() and kcache.shape[1] == kv_heads and kcache.shape[3] == dk
+            assert vcache.shape[:3] == kcache.shape[:3] and vcache.shape[3] == dv
+            page = kcache.shape[2]
+        if v_first is not None:
+            assert v_first.shape[0] >= n and v_first.shape[1] == kv_heads * dv
+        lib = self.lib()
+        self._check(lib.llm_qkv_prep(_ptr(parts), c_int(parts.shape[0]), c_longlong(parts.stride(0)), c_int(parts.shape[2]), c_int(heads),
+                                     c_int(kv_heads), c_int(dk), c_int(dv), c_int(rot_dims), _ptr(q_norm), _ptr(k_norm), c_float(eps),
+                                     _ptr(cos), _ptr(sin), _ptr(batch.positions), _ptr(batch.token_seq), _ptr(block_table),
+                                     c_int(block_table.shape[1]), _ptr(q_out), c_longlong(q_out.stride(0)), _ptr(kcache), _ptr(vcache),
+                                     c_int(page), c_int(mix_role), _ptr(mix_weight), _ptr(v_first), c_int(dtype_code(q_out.dtype)),
+                                     c_int(n), _stream()), lib)
+
+    def gated_attention(self, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, batch, block_table: torch.Tensor,
+                        out: torch.Tensor, nq: int, nkv: int, dk: int, dv: int, scale: float, window: int = 0, chunk: int = 0,
+                        sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, gate_off: int = 0) -> torch.Tensor:
+        """Causal attention of every token of the step over the cache positions of its request from the later of the window's
+        and the chunk's start (chunks are [c * chunk, (c + 1) * chunk) in absolute positions; 0: none) up to its own; keys of dk
+        and values of dv numbers a head; sink (float32 [nq], optional): exp(sink[head]) is one more term of the softmax's
+        denominator; gate (float32 partial sums [p, n, width], optional): the result times sigmoid(sum_p gate[p, t, gate_off +
+        head * dv + d]). q rows of [nq * dk]; out [n, nq * dv]."""
+        _need(q, "attention.q"); _need(kcache, "attention.kcache", q.dtype); _need(vcache, "attention.vcache", q.dtype)
+        _need(out, "attention.out", q.dtype); _need(block_table, "attention.block_table", torch.int32)
+        assert kcache.is_contiguous() and vcache.is_contiguous() and block_table.is_contiguous()
+        assert kcache.shape[1] == nkv and kcache.shape[3] == dk and vcache.shape[3] == dv
+        if sink is not None:
+            _need(sink, "attention.sink", torch.float32)
+            assert sink.numel() == nq and sink.is_contiguous()
+        gp, gs, gw = 0, 0, 0
+        if gate is not None:
+            _need(gate, "attention.gate", torch.float32)
+            assert gate.dim() == 3 and gate.is_contiguous()
+            gp, gs, gw = gate.shape[0], gate.stride(0), gate.shape[2]
+        page = kcache.shape[2]
+        if q.dtype == torch.bfloat16 and self.tensor_cores and self.gated_attention_tensor_cores:
+            lib = self.lib("tensorcore")
+            if lib.llm_gated_attention_mma_supported(c_int(nq), c_int(nkv), c_int(dk), c_int(dv), c_longlong(q.stride(0)), c_longlong(out.stride(0))):
+                self._check(lib.llm_gated_attention_mma(
+                    _ptr(q), c_longlong(q.stride(0)), _ptr(kcache), _ptr(vcache), _ptr(batch.seq_start), _ptr(batch.seq_ntok), _ptr(batch.seq_qoff),
+                    _ptr(block_table), c_int(block_table.shape[1]), _ptr(out), c_longlong(out.stride(0)), c_int(batch.n_seqs),
+                    c_int(batch.max_new_tokens), c_int(nq), c_int(nkv), c_int(dk), c_int(dv), c_int(page), c_float(scale), c_int(window),
+                    c_int(chunk), _ptr(sink), _ptr(gate), c_int(gp), c_longlong(gs), c_int(gw), c_int(gate_off), _stream()), lib)
+                return out
+        lib = self.lib()
+        self._check(lib.llm_gated_attention_simt(_ptr(q), c_longlong(q.stride(0)), _ptr(kcache), _ptr(vcache), c_int(dtype_code(q.dtype)),
+                                                 _ptr(batch.positions), _ptr(batch.token_seq), _ptr(block_table),
+                                                 c_int(block_table.shape[1]), _ptr(out), c_longlong(out.stride(0)), c_int(batch.n_tokens),
+                                                 c_int(nq), c_int(nkv), c_int(dk), c_int(dv), c_int(page), c_float(scale), c_int(window),
+                                                 c_int(chunk), _ptr(sink), _ptr(gate), c_int(gp), c_longlong(gs), c_int(gw), c_int(gate_off),
+                                                 _stream()), lib)
+        return out
+
+    def gated_attention_kernel(self, nq: int, nkv: int, dk: int, dv: int) -> str:
+        """What a bfloat16 model's gated attention of this geometry runs on: "tensor cores" or "CUDA cores"."""
+        if self.tensor_cores and self.gated_attention_tensor_cores:
+            lib = self.lib("tensorcore")
+            if lib.llm_gated_attention_mma_supported(c_int(nq), c_int(nkv), c_int(dk), c_int(dv), c_longlong(nq * dk), c_longlong(nq * dv)):
+                return "tensor cores"
+        return "CUDA cores"
+
+    # ------------------------------------------------------------------ selective scan
+    def conv_silu(self, parts: torch.Tensor, x_off: int, channels: int, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                  conv_state: torch.Tensor, batch, out: torch.Tensor) -> torch.Tensor:
+        """out[t, c] = silu(bias[c] + sum_j weight[c, j] * x[t - (K - 1) + j, c]) over each request's own tokens, x = columns
+        x_off .. x_off + channels of the float32 sums `parts` [p, n, width]; inputs before the step's portion come from
+        conv_state [slots, K - 1, channels] (float32) at the request's slot, which afterwards holds the request's last K - 1
+        inputs."""
+        _need(parts, "conv.parts", torch.float32); _need(weight, "conv.weight", out.dtype); _need(conv_state, "conv.state", torch.float32)
+        _need(out, "conv.out")
+        K = weight.shape[1]
+        n = batch.n_tokens
+        assert parts.dim() == 3 and parts.is_contiguous() and weight.is_contiguous() and weight.shape[0] == channels
+        assert conv_state.is_contiguous() and tuple(conv_state.shape[1:]) == (K - 1, channels)
+        assert out.is_contiguous() and out.shape[0] >= n and out.shape[1] == channels
+        if bias is not None:
+            _need(bias, "conv.bias", torch.float32)
+            assert bias.numel() == channels
+        lib = self.lib()
+        self._check(lib.llm_conv_silu(_ptr(parts), c_int(parts.shape[0]), c_longlong(parts.stride(0)), c_int(parts.shape[2]), c_int(x_off),
+                                      c_int(channels), c_int(K), _ptr(weight), _ptr(bias), _ptr(conv_state), _ptr(batch.token_seq),
+                                      _ptr(batch.seq_qoff), _ptr(batch.seq_ntok), _ptr(batch.seq_slot), _ptr(out),
+                                      c_int(dtype_code(out.dtype)), c_int(n), c_int(batch.n_seqs), _stream()), lib)
+        if K > 1:
+            self.launches += 1  # the kernel that renews the slot
+        return out
+
+    def dt_softplus(self, proj: torch.Tensor, rank: int, weight_t: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                    n_tokens: int) -> torch.Tensor:
+        """out[t, c] (float32) = softplus(bias[c] + sum_r weight_t[r, c] * proj[t, r]) for the first `rank` columns of the
+        float32 rows proj; weight_t [rank, channels] is the map stored transposed."""
+        _need(proj, "dt.proj", torch.float32); _need(weight_t, "dt.weight"); _need(out, "dt.out", torch.float32)
+        C = weight_t.shape[1]
+        assert weight_t.is_contiguous() and weight_t.shape[0] == rank and out.is_contiguous() and out.shape[1] == C and out.shape[0] >= n_tokens
+        if bias is not None:
+            _need(bias, "dt.bias", torch.float32)
+            assert bias.numel() == C
+        lib = self.lib()
+        self._check(lib.llm_dt_softplus(_ptr(proj), c_longlong(proj.stride(0)), c_int(rank), _ptr(weight_t), _ptr(bias), c_int(C), _ptr(out),
+                                        c_int(dtype_code(weight_t.dtype)), c_int(n_tokens), _stream()), lib)
+        return out
+
+    def selective_scan(self, xc: torch.Tensor, dt: torch.Tensor, proj: torch.Tensor, b_off: int, c_off: int, state_size: int,
+                       zparts: torch.Tensor, z_off: int, a_log: torch.Tensor, skip: Optional[torch.Tensor], state: torch.Tensor, batch,
+                       out: torch.Tensor) -> torch.Tensor:
+        """Token after token of every request: S[c, n] <- exp(dt[t, c] * A[c, n]) * S[c, n] + dt[t, c] * xc[t, c] * B[t, n],
+        y[t, c] = sum_n S[c, n] * C[t, n] + skip[c] * xc[t, c], out[t, c] = y * silu(z[t, c]); A = -exp(a_log) [channels, N];
+        B, C = columns b_off.., c_off.. of the float32 rows proj; z = columns z_off.. of the float32 sums zparts [p, n, width];
+        state [slots, channels, N] float32, read from and written to the request's slot."""
+        _need(xc, "scan.x"); _need(dt, "scan.dt", torch.float32); _need(proj, "scan.proj", torch.float32)
+        _need(zparts, "scan.z", torch.float32); _need(a_log, "scan.a_log", torch.float32); _need(state, "scan.state", torch.float32)
+        _need(out, "scan.out", xc.dtype)
+        C, N = a_log.shape
+        assert N == state_size and xc.is_contiguous() and dt.is_contiguous() and out.is_contiguous() and a_log.is_contiguous()
+        assert xc.shape[1] == C and dt.shape[1] == C and out.shape[1] == C and state.is_contiguous() and tuple(state.shape[1:]) == (C, N)
+        assert zparts.dim() == 3 and zparts.is_contiguous()
+        if skip is not None:
+            _need(skip, "scan.skip", torch.float32)
+            assert skip.numel() == C
+        lib = self.lib()
+        self._check(lib.llm_selective_scan(_ptr(xc), _ptr(dt), _ptr(proj), c_longlong(proj.stride(0)), c_int(b_off), c_int(c_off),
+                                           _ptr(zparts), c_int(zparts.shape[0]), c_longlong(zparts.stride(0)), c_int(zparts.shape[2]),
+                                           c_int(z_off), _ptr(a_log), _ptr(skip), _ptr(state), _ptr(batch.seq_qoff), _ptr(batch.seq_ntok),
+                                           _ptr(batch.seq_slot), c_int(C), c_int(N), _ptr(out), c_int(dtype_code(xc.dtype)),
+                                           c_int(batch.n_seqs), _stream()), lib)
         return out
 
     # ------------------------------------------------------------------ sampling

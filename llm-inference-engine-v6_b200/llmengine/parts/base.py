@@ -83,6 +83,9 @@ class Residual:
         # are and the scalar be multiplied in where that product's results are consumed (ops.RowScale).
         self.prescaled: Optional[torch.Tensor] = None
         self.prescaled_weight: Optional[torch.Tensor] = None  # the weight tensor prescaled was made with
+        # the stream itself in the engine dtype, if whoever wrote the stream last left it (a block whose sub-layers read the
+        # stream without a norm before them); None once the stream has moved on
+        self.operand: Optional[torch.Tensor] = None
 
 
 @dataclass

@@ -1,12 +1,16 @@
 """Arrangement of parts in a layer. "pre_norm": h += mixer(norm1(h)); h += feed_forward(norm2(h))
 (src/engine.cpp:307-413). The residual sums are fused into the norm that follows them.
 "parallel": h += mixer(norm1(h)) + feed_forward(norm2(h)), both norms of the same h; then an optional
-input from the tokens themselves, h += token_input(h)."""
+input from the tokens themselves, h += token_input(h).
+"post_norm": the sub-layers read h itself and the norms sit on their outputs, each followed by an optional per-column
+layer scale: h += scale1 * norm1(mixer(h)); h += scale2 * norm2(feed_forward(h))."""
 from __future__ import annotations
 
 from typing import List
 
-from .base import Block, LayerCache, Residual
+import torch
+
+from .base import Block, LayerCache, Norm, Residual
 from .registry import build_part, part_class, register_part
 from .spec import BlockSpec, TensorNeed
 
@@ -116,14 +120,80 @@ class ParallelBlock(Block):
                 res.pending = a
             else:
                 ops.stream_add(res.h, a, b, n_rows=n)
-            res.sumsq = res.prescaled = res.prescaled_weight = None
+            res.sumsq = res.prescaled = res.prescaled_weight = res.operand = None
             return res
         xs = ctx.ws.get("block.stream_copy", (n, res.h.shape[1]), self.env.dtype)
         ops.stream_add(res.h, a, b, copy=xs, n_rows=n)
-        res.sumsq = res.prescaled = res.prescaled_weight = None
+        res.sumsq = res.prescaled = res.prescaled_weight = res.operand = None
         res.pending = self.token_input.forward(xs, ctx)
         return res
 
 
+class PostNormBlock(Block):
+    """h += scale1 * norm1(mixer(h)); h += scale2 * norm2(feed_forward(h)): the sub-layers read the stream itself (in the
+    engine precision, as the operand of their first product), the norms (of the form weight * y / rms(y)) sit on their
+    results. One kernel a sub-layer takes the result's partial sums, normalises, scales, adds into the float32 stream and
+    leaves the stream in the engine precision for the next reader."""
+
+    def __init__(self, spec: BlockSpec, env):
+        super().__init__(spec, env)
+        self.norm1 = build_part("norm", spec.norm1, env)
+        self.mixer = build_part("mixer", spec.mixer, env)
+        self.feed_forward = self.norm2 = None
+        if spec.feed_forward is not None:
+            self.norm2 = build_part("norm", spec.norm2, env)
+            self.feed_forward = build_part("feed_forward", spec.feed_forward, env)
+        for norm in (self.norm1, self.norm2):
+            if norm is not None and type(norm).prescale_weight is Norm.prescale_weight:  # not a norm that can be applied as weight * y * s(row)
+                raise ValueError("a post-norm block needs norms of the form weight * y / rms(y)")
+        self.scale1 = self.scale2 = None
+
+    @staticmethod
+    def tensor_needs(spec: BlockSpec) -> List[TensorNeed]:
+        out: List[TensorNeed] = []
+        subs = [("norm", spec.norm1), ("mixer", spec.mixer)]
+        if spec.feed_forward is not None:
+            subs += [("norm", spec.norm2), ("feed_forward", spec.feed_forward)]
+        for cat, sub in subs:
+            out += part_class(cat, sub.kind).tensor_needs(sub)
+        if spec.scale1:
+            out.append(TensorNeed(spec.scale1, (spec.norm1.dim,), "float32", init="around_one"))
+        if spec.scale2 and spec.feed_forward is not None:
+            out.append(TensorNeed(spec.scale2, (spec.norm2.dim,), "float32", init="around_one"))
+        return out
+
+    def subparts(self):
+        return tuple(p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None)
+
+    def cache_needs(self):
+        return self.mixer.cache_needs()
+
+    def load(self, tensors) -> None:
+        for p in self.subparts():
+            p.load(tensors)
+        self.scale1 = tensors[self.spec.scale1] if self.spec.scale1 else None
+        self.scale2 = tensors[self.spec.scale2] if (self.spec.scale2 and self.feed_forward is not None) else None
+
+    def forward(self, res: Residual, ctx, cache: LayerCache) -> Residual:
+        ops, n, dt = self.env.ops, ctx.n_tokens, self.env.dtype
+        ctx.residual = ctx.next_norm = None  # the parts' last products return their sums; nobody adds into the stream
+        same = dt == torch.float32  # the 32-bit engine reads the stream as it is
+        xs = res.h if same else ctx.ws.get("block.stream_copy", (n, res.h.shape[1]), dt)
+        if res.pending is not None or not (same or (res.operand is not None and res.operand.data_ptr() == xs.data_ptr())):
+            # what an earlier block left pending is added, and the stream in the engine precision is made, unless the block
+            # before this one was of this kind and has left it (its last kernel writes it)
+            ops.stream_add(res.h, res.pending, None, copy=None if same else xs, n_rows=n)
+            res.pending = None
+        res.sumsq = res.prescaled = res.prescaled_weight = None
+        a = self.mixer.forward(xs, ctx, cache)
+        ops.norm_add(res.h, a, None, self.norm1.weight, self.scale1, self.norm1.spec.eps, copy=None if same else xs, n_rows=n)
+        if self.feed_forward is not None:
+            b = self.feed_forward.forward(xs, ctx)
+            ops.norm_add(res.h, b, None, self.norm2.weight, self.scale2, self.norm2.spec.eps, copy=None if same else xs, n_rows=n)
+        res.operand = None if same else xs  # valid until somebody else writes the stream
+        return res
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "post_norm", PostNormBlock)
 register_part("block", "parallel", ParallelBlock)

@@ -32,6 +32,9 @@ class TokenLookup(Embedding):
     def forward(self, ctx) -> torch.Tensor:
         ops, n = self.env.ops, ctx.n_tokens
         h = ctx.ws.get("model.residual", (n, self.spec.dim), torch.float32)
+        scale = float(getattr(self.spec, "scale", 1.0))
+        if scale != 1.0:
+            return ops.embed(self.table, ctx.token_ids, h, scale=scale)
         nxt = getattr(ctx, "next_norm", None)
         wn = nxt.prescale_weight() if nxt is not None else None
         if (self.env.dtype == torch.bfloat16 and getattr(ops, "meet_products", False) and n <= 64 and wn is not None and
@@ -52,7 +55,8 @@ class TokenLookup(Embedding):
 
 
     def lookup(self, ctx, out: torch.Tensor) -> torch.Tensor:
-        return self.env.ops.embed(self.table, ctx.token_ids, out)
+        scale = float(getattr(self.spec, "scale", 1.0))
+        return self.env.ops.embed(self.table, ctx.token_ids, out, **({} if scale == 1.0 else {"scale": scale}))
 
 
 class LinearHead(Head):

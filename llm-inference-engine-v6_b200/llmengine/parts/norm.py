@@ -36,7 +36,7 @@ class RMSNorm(Norm):
         self.env.ops.rmsnorm(res.h, self.weight, self.spec.eps, out, delta=res.pending, rows=rows, n_rows=n)
         if rows is None:
             if res.pending is not None:
-                res.sumsq = res.prescaled = res.prescaled_weight = None  # the stream has moved on
+                res.sumsq = res.prescaled = res.prescaled_weight = res.operand = None  # the stream has moved on
             res.pending = None
         return out
 

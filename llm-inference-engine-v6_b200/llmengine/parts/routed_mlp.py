@@ -16,8 +16,8 @@ from typing import List
 import torch
 
 from .base import FeedForward, NormalizedRows
-from .registry import register_part
-from .spec import RoutedMLPSpec, TensorNeed
+from .registry import build_part, part_class, register_part
+from .spec import GroupRoutedMLPSpec, RoutedMLPSpec, TensorNeed
 
 
 class RoutedMLP(FeedForward):
@@ -72,4 +72,93 @@ class RoutedMLP(FeedForward):
         return ops.routed_combine(y, out, s.top)
 
 
+class GroupRoutedMLP(FeedForward):
+    """Gated experts chosen by scores over all experts, with a correction that only the choice sees and a limit on groups
+    of experts (GroupRoutedMLPSpec), plus an optional expert that every token goes through:
+
+        s = softmax(Wr x)  (float32);  choice = s + correction;  only the best `keep_groups` of `groups` groups stay
+        chosen = the `top` largest choice scores;  g_e = s_e / (sum of the chosen s + norm_eps)
+        out = sum_e g_e * Wdown_e (silu(Wgate_e x) * Wup_e x)  +  shared(x)
+
+    An expert's gate and up rows are stored in turn ([E, 2 ff, hidden]: row 2 f the gate, row 2 f + 1 its up row), so that the
+    per-expert product has both in one thread's hands and applies silu(gate) * up in its epilogue. Returns the routed sum and
+    the shared expert's product as two sets of partial sums, [2 or more, tokens, hidden], for the next reader to add."""
+
+    def __init__(self, spec: GroupRoutedMLPSpec, env):
+        super().__init__(spec, env)
+        if spec.activation != "silu":
+            raise ValueError(f"routed gated feed-forward: activation '{spec.activation}' is not implemented (silu is)")
+        if not (1 <= spec.top <= spec.experts):
+            raise ValueError(f"routed feed-forward: cannot choose {spec.top} of {spec.experts} experts")
+        if spec.groups < 1 or spec.experts % spec.groups or not (1 <= spec.keep_groups <= spec.groups):
+            raise ValueError(f"routed feed-forward: {spec.experts} experts do not form {spec.groups} equal groups of which {spec.keep_groups} stay")
+        if spec.keep_groups * (spec.experts // spec.groups) < spec.top:
+            raise ValueError("routed feed-forward: the groups that stay hold fewer experts than a token uses")
+        if not (len(spec.gate_weights) == len(spec.up_weights) == len(spec.down_weights) == spec.experts):
+            raise ValueError("routed feed-forward: one gate, one up and one down matrix per expert")
+        self.shared = build_part("feed_forward", spec.shared, env) if spec.shared is not None else None
+        self.router = self.correction = self.w_gate_up = self.w_down = None
+
+    @staticmethod
+    def tensor_needs(spec: GroupRoutedMLPSpec) -> List[TensorNeed]:
+        out = [TensorNeed(spec.router_weight, (spec.experts, spec.hidden))]
+        if spec.correction:
+            out.append(TensorNeed(spec.correction, (spec.experts,), "float32", init="zeros"))
+        for g, u, d in zip(spec.gate_weights, spec.up_weights, spec.down_weights):
+            out += [TensorNeed(g, (spec.intermediate, spec.hidden)), TensorNeed(u, (spec.intermediate, spec.hidden)),
+                    TensorNeed(d, (spec.hidden, spec.intermediate))]
+        if spec.shared is not None:
+            out += part_class("feed_forward", spec.shared.kind).tensor_needs(spec.shared)
+        return out
+
+    def subparts(self):
+        return (self.shared,) if self.shared is not None else ()
+
+    def kernel_notes(self):
+        s = self.spec
+        if self.env.dtype == torch.bfloat16 and (s.hidden % 8 or s.intermediate % 8):
+            return [f"routed feed-forward: sizes {s.hidden} and {s.intermediate} are not both multiples of 8: the per-expert "
+                    "products run on CUDA cores"]
+        return []
+
+    def load(self, tensors) -> None:
+        s = self.spec
+        self.router = tensors[s.router_weight]
+        self.correction = tensors[s.correction] if s.correction else None
+        gu = [torch.stack([tensors[g], tensors[u]], dim=1).reshape(2 * s.intermediate, s.hidden) for g, u in zip(s.gate_weights, s.up_weights)]
+        self.w_gate_up = torch.stack(gu).contiguous()                                  # [E, 2 ff, hidden], gate and up rows in turn
+        self.w_down = torch.stack([tensors[n] for n in s.down_weights]).contiguous()  # [E, hidden, ff]
+        if self.shared is not None:
+            self.shared.load(tensors)
+
+    def forward(self, x, ctx) -> torch.Tensor:
+        s, ops, n, dt = self.spec, self.env.ops, ctx.n_tokens, self.env.dtype
+        if isinstance(x, NormalizedRows):
+            x = x.dense(ctx)
+        x = x[:n]
+        idx = ctx.ws.get("routed.idx", (n, s.top), torch.int32)
+        share = ctx.ws.get("routed.share", (n, s.top), torch.float32)
+        ops.route_grouped(x, self.router, self.correction, s.top, s.groups, s.keep_groups, s.norm_eps, idx, share)
+        tile = ops.routed_tile_rows(n, dt, (s.hidden, s.intermediate), n * s.top / s.experts)
+        tile_expert, tile_rows = ops.routed_group(idx, s.experts, tile, ctx.ws, "routed")
+        act = ctx.ws.get("routed.act", (n * s.top, s.intermediate), dt)
+        ops.routed_product(x, s.top, self.w_gate_up, tile_expert, tile_rows, act, "silu_pairs")
+        y = ctx.ws.get("routed.y", (n * s.top, s.hidden), torch.float32)
+        ops.routed_product(act, 1, self.w_down, tile_expert, tile_rows, y, "share", share=share.view(-1))
+        if self.shared is None:
+            out = ctx.ws.get("routed.delta", (n, s.hidden), torch.float32)
+            return ops.routed_combine(y, out, s.top)
+        # the shared expert's last product, as it comes (it works for no stream here: its sums are added to the routed sum)
+        keep = ctx.residual
+        ctx.residual = None
+        b = self.shared.forward(x, ctx)
+        ctx.residual = keep
+        b = b if b.dim() == 3 else b.unsqueeze(0)
+        out = ctx.ws.get("routed.delta", (1 + b.shape[0], n, s.hidden), torch.float32)
+        ops.routed_combine(y, out[0], s.top)
+        out[1:].copy_(b)
+        return out
+
+
 register_part("feed_forward", "routed_mlp", RoutedMLP)
+register_part("feed_forward", "group_routed_mlp", GroupRoutedMLP)

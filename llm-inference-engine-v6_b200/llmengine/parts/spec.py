@@ -113,6 +113,63 @@ class AttentionSpec:
 
 
 @dataclass(frozen=True)
+class GatedAttentionSpec:
+    """Causal grouped-query attention with keys of `head_dim` and values of `value_dim` numbers a head (kind "gated_attention",
+    parts/gated_attention.py). Options, each off when its field is None / 0 / False:
+    q_norm, k_norm: RMS norm of every query / key head over head_dim with one weight [head_dim] for all heads, before the rotation;
+    position: a position spec with rotation tables over the first `dims` <= head_dim numbers of a head;
+    chunk: position i sees j <= i only if floor(i / chunk) == floor(j / chunk) (chunk borders are absolute positions);
+    window: the last `window` keys; sink: a number per head whose exponential is one more term of the softmax's denominator;
+    value_mix: "first" = this layer's values are kept for the step's tokens, "mix" = v <- (1 - m) v + m v_first with the scalar
+    tensor `value_mix_weight` and the values of the step's "first" layer (the mixed values are cached);
+    gate_weight: the heads' outputs are multiplied by sigmoid(Wg h) before the output projection."""
+    kind: str
+    hidden: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    eps: float
+    position: object
+    q_weight: str
+    k_weight: str
+    v_weight: str
+    o_weight: str
+    q_norm: Optional[str] = None
+    k_norm: Optional[str] = None
+    sink: Optional[str] = None
+    gate_weight: Optional[str] = None
+    value_mix: Optional[str] = None        # None | "first" | "mix"
+    value_mix_weight: Optional[str] = None
+    chunk: int = 0
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class SelectiveScanSpec:
+    """A recurrent mixer with input-dependent decay (kind "selective_scan", parts/selective_scan.py): [x | z] = W_in h;
+    x <- silu(causal convolution over `taps` inputs a channel, with bias); [dt_low: dt_rank | B: state | C: state] = W_x x;
+    dt = softplus(W_dt dt_low + dt_bias); S <- exp(dt A) S + dt x B, A = -exp(a_log); y = S C + skip x; out = W_o (y silu(z)).
+    The state (S [inner, state] and the convolution's last taps - 1 inputs) is float32 and kept per request."""
+    kind: str
+    hidden: int
+    inner: int
+    state: int
+    taps: int
+    dt_rank: int
+    in_weight: str
+    conv_weight: str
+    conv_bias: str
+    x_weight: str
+    dt_weight: str
+    dt_bias: str
+    a_log: str
+    skip: str
+    o_weight: str
+
+
+@dataclass(frozen=True)
 class GatedMLPSpec:
     """down( act(gate(x)) * up(x) ), dense, no bias. activation "silu"."""
     kind: str
@@ -142,6 +199,30 @@ class RoutedMLPSpec:
 
 
 @dataclass(frozen=True)
+class GroupRoutedMLPSpec:
+    """Mixture of gated experts with scores over all experts (kind "group_routed_mlp"): s = softmax(router x) in float32;
+    choice scores = s + correction (optional tensor [experts]); the experts form `groups` equal groups of neighbours, a group's
+    score is its largest choice score, and only experts of the best `keep_groups` groups can be chosen; the `top` largest
+    choice scores win; their weights are s (without the correction) divided by (their sum + norm_eps); an expert is
+    down_e(act(gate_e x) * up_e x) without biases; `shared` (a GatedMLPSpec or None) runs for every token and is added."""
+    kind: str
+    hidden: int
+    intermediate: int
+    experts: int
+    top: int
+    router_weight: str
+    correction: Optional[str]
+    gate_weights: Tuple[str, ...]
+    up_weights: Tuple[str, ...]
+    down_weights: Tuple[str, ...]
+    groups: int = 1
+    keep_groups: int = 1
+    norm_eps: float = 1e-20
+    activation: str = "silu"
+    shared: object = None
+
+
+@dataclass(frozen=True)
 class TokenSideSpec:
     """A per-layer input from the token itself, added after the layer: e = table[token, col0 : col0 + dim];
     y = proj(gelu_tanh(gate(x)) * e) for the stream x; x += y / rms(y) * norm (eps inside the root)."""
@@ -163,6 +244,9 @@ class BlockSpec:
     """kind "pre_norm": h += mixer(norm1(h)); h += feed_forward(norm2(h)).
     kind "parallel": h += mixer(norm1(h)) + feed_forward(norm2(h)), both of the same h (feed_forward and norm2 may be
     None: then the mixer alone); then, if `token_input` is given, h += token_input(h, tokens).
+    kind "post_norm": the norms sit on the sub-layers' outputs and the sub-layers read h itself:
+    h += scale1 * norm1(mixer(h)); h += scale2 * norm2(feed_forward(h)) (feed_forward and norm2 may be None); scale1 / scale2 name
+    optional per-column layer-scale tensors [hidden].
     mixer / feed_forward / token_input are any registered spec objects with a `kind`."""
     kind: str
     norm1: object
@@ -170,6 +254,8 @@ class BlockSpec:
     norm2: object
     feed_forward: object
     token_input: object = None
+    scale1: Optional[str] = None
+    scale2: Optional[str] = None
 
 
 @dataclass(frozen=True)
@@ -184,11 +270,12 @@ class LayerRun:
 
 @dataclass(frozen=True)
 class EmbeddingSpec:
-    """kind "lookup": residual stream row = table row of the token id, widened to float32."""
+    """kind "lookup": residual stream row = table row of the token id, widened to float32, times `scale`."""
     weight: str
     vocab_size: int
     dim: int
     kind: str = "lookup"
+    scale: float = 1.0
 
 
 @dataclass(frozen=True)
