@@ -112,7 +112,7 @@ def write_safetensors(path: str, tensors: Dict[str, torch.Tensor]) -> None:
         t = tensors[name].detach().cpu().contiguous()
         if t.dtype not in _NAMES:
             raise SafetensorsError(f"cannot write dtype {t.dtype} of {name}")
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""  # (a scalar has no last dimension to view)
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
         blobs.append(raw)
         off += len(raw)

@@ -132,15 +132,15 @@ def attention_mixer(h, w, p, m, eps, start, state, shared):
     for t in range(T):
         i = start + t
         lo = (i // chunk) * chunk if chunk > 0 else 0
+        keys, vals = torch.stack(state["k"][lo:i + 1]), torch.stack(state["v"][lo:i + 1])  # [n, G, dk], [n, G, dv]
         for a in range(H):
             g = a // (H // G)
-            s = torch.stack([(q[t, a] * state["k"][j][g]).sum() * scale for j in range(lo, i + 1)])
+            s = (keys[:, g] @ q[t, a]) * scale
             sink = w[p + "sink"][a]
             top = torch.maximum(s.max(), sink)
             e = torch.exp(s - top)
-            denom = e.sum() + torch.exp(sink - top)
-            for n, j in enumerate(range(lo, i + 1)):
-                out[t, a] += e[n] / denom * state["v"][j][g]
+            denom = e.sum() + torch.exp(sink - top)  # the sink: one more term below the line, nothing above it
+            out[t, a] = (e / denom) @ vals[:, g]
     gate = torch.sigmoid(h @ w[p + "g"].T)
     return (out.reshape(T, H * dv) * gate) @ w[p + "o"].T
 
@@ -244,3 +244,19 @@ class PlainZulopel:
                 layers_out.append(x.clone())
         state["len"] = start + len(tokens)
         return rms_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+def forward(cfg, w, tokens):
+    """Logits [T, vocab] of one whole sequence."""
+    return PlainZulopel(cfg, w).forward(tokens, {})
+
+
+def generate(cfg, w, prompt, n_new):
+    """Greedy: the first index of the largest logit, token by token through the carried state."""
+    m, state = PlainZulopel(cfg, w), {}
+    out = list(prompt)
+    logits = m.forward(out, state)
+    for _ in range(n_new):
+        out.append(int(torch.argmax(logits[-1])))
+        logits = m.forward(out[-1:], state)
+    return out
