@@ -462,6 +462,27 @@ DESIGN_SIZES = {
 }
 
 
+def zulopel_sizes(width, heads, kv_heads, dim, vdim, chunk, inner, state, dt_rank, experts, top, groups, keep, expert_ff, shared_ff, layers, vocab):
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "v_mix": True, "mask": {"size": chunk},
+           "rot": {"dims": dim // 2, "base": 500000.0, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    scan = {"inner": inner, "state": state, "conv": 4, "dt_rank": dt_rank}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top, "groups": {"count": groups, "keep": keep}},
+           "shared": {"ff": shared_ff}}
+    return {"architecture": "Zulopel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": width ** 0.5},
+            "max_positions": 8192,
+            "layers": [{"type": "mamba1", "mixer": scan, "mlp": moe} if i % 2 == 0 else {"type": "attention", "mixer": att, "mlp": moe}
+                       for i in range(layers)]}
+
+
+# Zulopel: selective-scan and gated-attention layers in turn, every layer with routed gated experts and a shared expert; beside it
+# the Vapelix configuration (attention + routed experts: the closest existing model) and the Llama one of the same name above
+ZULOPEL_SIZES = {
+    "w1024": (zulopel_sizes(1024, 16, 4, 64, 64, 1024, 2048, 16, 64, 8, 2, 4, 2, 1408, 1408, 4, 32768), DESIGN_SIZES["w1024"][0]),
+    "w2048": (zulopel_sizes(2048, 32, 8, 64, 64, 1024, 4096, 16, 128, 16, 4, 4, 2, 2048, 2048, 4, 32768), DESIGN_SIZES["w2048"][0]),
+}
+DESIGNS = {"vapelix": DESIGN_SIZES, "zulopel": ZULOPEL_SIZES}
+
+
 def run_design(args):
     """Prompt and decode throughput of another design at sizes that resemble a real model's layers (random weights),
     beside the Llama decoder of equal width, depth and feed-forward rows a token: one JSON line a size."""
@@ -536,14 +557,16 @@ def run_design(args):
                 "launches_per_decode_step": round(eng.ops.launches / K, 1), "weight_bytes": eng.model.weight_bytes,
                 "cache_bytes_per_token": eng.model.kv_bytes_per_token()}
 
-    for name in (args.sizes.split(",") if args.sizes else sorted(DESIGN_SIZES)):
-        design_cfg, llama_cfg = DESIGN_SIZES[name]
+    sizes = DESIGNS[args.design]
+    for name in (args.sizes.split(",") if args.sizes else sorted(sizes)):
+        design_cfg, other_cfg = sizes[name]
+        other = other_cfg.get("architecture", "llama").lower()
         clocks = ClockSampler()
         clocks.start()
         rec = {"bench": "design beside the closest existing model", "design": args.design, "sizes": name, "dtype": "bf16",
                "data": "synthetic: random weights N(0,0.02), uniform random token ids", "batch": B, "context": CONTEXT,
                "prefill_tokens": PREFILL_TOKENS, "steps": K, "warmup": W,
-               args.design: measure(design_cfg, design_cfg["vocab"]), "llama": measure(llama_cfg, llama_cfg["vocab_size"])}
+               args.design: measure(design_cfg, design_cfg["vocab"]), other: measure(other_cfg, other_cfg.get("vocab", other_cfg.get("vocab_size")))}
         rec["clocks"] = clocks.stop()
         print(json.dumps(rec), flush=True)
     return 0
@@ -565,10 +588,10 @@ def main():
     ap.add_argument("--workload", choices=["decode", "serve", "long"], default="decode",
                     help="decode: the contract's line (default). serve / long: the workloads of the 3B and 8B configurations, a line of their own")
     ap.add_argument("--budget", type=int, default=2048, help="serve: prompt tokens a step (max_prefill_tokens_per_step)")
-    ap.add_argument("--design", choices=["vapelix"], default=None,
+    ap.add_argument("--design", choices=sorted(DESIGNS), default=None,
                     help="instead of the default line: prompt and decode throughput of this design at a few layer sizes, "
-                         "beside the Llama decoder of equal size (one JSON line a size)")
-    ap.add_argument("--sizes", default="", help="--design: comma list of " + ",".join(sorted(DESIGN_SIZES)) + " (default: all)")
+                         "beside the closest existing model of equal size (one JSON line a size)")
+    ap.add_argument("--sizes", default="", help="--design: comma list of the design's sizes, e.g. w1024,w2048 (default: all)")
     ap.add_argument("--reference-setup-limit", type=float, default=900.0, help="seconds the reference arm may spend filling contexts")
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:

@@ -12,6 +12,11 @@
 // boundaries); every split writes a normalised partial output with its (max, sum) and a second
 // kernel merges the splits in index order.
 //
+// Options for mixers that want them, each off at 0 / null: keys and values of different sizes (HDK, HDV); `chunk`: a row at
+// position i reads only keys j with floor(j / chunk) == floor(i / chunk); `sink`: a float per query head whose exponential
+// is one more term of the softmax's denominator; `gate`: float32 partial sums whose sigmoid multiplies the result before
+// it is rounded (all three in the form without splits).
+//
 // Formula: the reference's attention_f32 (src/kernels.cpp:413-474): kv head = q head / group,
 // score = (q . k) * scale applied after the dot, softmax, weighted sum of values.
 #include "common.cuh"
@@ -28,20 +33,21 @@ struct AttnParams {
   const bf16* kcache; const bf16* vcache;
   const int* seq_start; const int* seq_ntok; const int* seq_qoff; const int* block_table;
   int max_blocks, nq, nkv, page_size, window;
+  int chunk; const float* sink; const float* gate; int g_parts; long long g_pstride; int g_width, g_off;
   float scale;
   bf16* out; long long ld_out;
   // split mode (decode): partial outputs [split][token][head][HD] and (max, sum) [split][token][head][2]
   float* part_o; float* part_ml; int split_keys, n_splits; long long part_stride_tokens;
 };
 
-template <int HD, bool SPLIT>
+template <int HD, int HDV, bool SPLIT>  // HD: numbers of a query / key head; HDV: of a value head
 __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const AttnParams p) {
-  constexpr int LD = HD + 8;  // padded row (elements): 16-byte shifts keep ldmatrix free of bank conflicts
-  constexpr int KSTEPS = HD / 16, DTILES = HD / 8;
+  constexpr int LD = HD + 8, LDV = HDV + 8;  // padded rows (elements): 16-byte shifts keep ldmatrix free of bank conflicts
+  constexpr int KSTEPS = HD / 16, DTILES = HDV / 8;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);     // [M_TILE][LD]
   bf16* k_s = q_s + M_TILE * LD;                     // [2][N_TILE][LD]
-  bf16* v_s = k_s + 2 * N_TILE * LD;                 // [2][N_TILE][LD]
+  bf16* v_s = k_s + 2 * N_TILE * LD;                 // [2][N_TILE][LDV]
 
   dep_launch();
   dep_wait();
@@ -60,13 +66,14 @@ __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Attn
   const int pos0 = p.seq_start[seq] + q0;      // position of the tile's first token
   const int pos_last = pos0 + n_tq - 1;
   int lo = (p.window > 0) ? max(0, pos0 - p.window + 1) : 0;  // oldest key any row reads
+  if (p.chunk > 0) lo = max(lo, (pos0 / p.chunk) * p.chunk);  // (the first token's chunk begins before the others')
   int hi = pos_last;                                          // newest key any row reads
   if (SPLIT) {
     lo = max(lo, split * p.split_keys);
     hi = min(hi, (split + 1) * p.split_keys - 1);
   }
   const int* table = p.block_table + (size_t)seq * p.max_blocks;
-  const size_t head_stride = (size_t)p.page_size * HD;
+  const size_t head_stride = (size_t)p.page_size * HD, head_stride_v = (size_t)p.page_size * HDV;
 
   // ---- Q tile -> shared memory (rows beyond n_rows are zeros)
   for (int c = tid; c < M_TILE * (HD / 8); c += THREADS) {
@@ -81,7 +88,7 @@ __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Attn
 
   auto load_tile = [&](int kt, int buf) {
     bf16* kd = k_s + buf * N_TILE * LD;
-    bf16* vd = v_s + buf * N_TILE * LD;
+    bf16* vd = v_s + buf * N_TILE * LDV;
     for (int c = tid; c < N_TILE * (HD / 8); c += THREADS) {
       const int r = c / (HD / 8), ch = c % (HD / 8);
       const int key = kt * N_TILE + r;
@@ -92,7 +99,20 @@ __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Attn
         off = ((size_t)page * p.nkv + kvh) * head_stride + (size_t)(key % p.page_size) * HD + ch * 8;
       }
       cp_async16(kd + r * LD + ch * 8, p.kcache + off, valid);
-      cp_async16(vd + r * LD + ch * 8, p.vcache + off, valid);
+      if (HDV == HD) cp_async16(vd + r * LDV + ch * 8, p.vcache + off, valid);
+    }
+    if (HDV != HD) {
+      for (int c = tid; c < N_TILE * (HDV / 8); c += THREADS) {
+        const int r = c / (HDV / 8), ch = c % (HDV / 8);
+        const int key = kt * N_TILE + r;
+        const bool valid = key >= lo && key <= hi;
+        size_t off = 0;
+        if (valid) {
+          const int page = table[key / p.page_size];
+          off = ((size_t)page * p.nkv + kvh) * head_stride_v + (size_t)(key % p.page_size) * HDV + ch * 8;
+        }
+        cp_async16(vd + r * LDV + ch * 8, p.vcache + off, valid);
+      }
     }
   };
 
@@ -109,7 +129,11 @@ __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Attn
   const int row_a = warp * 16 + lane / 4, row_b = row_a + 8;  // the two rows this thread holds
   const int pos_a = (row_a < n_rows) ? pos0 + row_a / g : -1;  // -1: padding row, sees no key
   const int pos_b = (row_b < n_rows) ? pos0 + row_b / g : -1;
-  const int lo_a = (p.window > 0) ? pos_a - p.window + 1 : 0, lo_b = (p.window > 0) ? pos_b - p.window + 1 : 0;
+  int lo_a = (p.window > 0) ? pos_a - p.window + 1 : 0, lo_b = (p.window > 0) ? pos_b - p.window + 1 : 0;
+  if (p.chunk > 0) {  // a row's own chunk: rows of one tile may lie on both sides of a chunk's edge
+    lo_a = max(lo_a, (max(pos_a, 0) / p.chunk) * p.chunk);
+    lo_b = max(lo_b, (max(pos_b, 0) / p.chunk) * p.chunk);
+  }
 
   float o_acc[DTILES][4];
 #pragma unroll
@@ -125,7 +149,7 @@ __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Attn
       cp_async_wait<1>();
       __syncthreads();
       const bf16* kb = k_s + buf * N_TILE * LD;
-      const bf16* vb = v_s + buf * N_TILE * LD;
+      const bf16* vb = v_s + buf * N_TILE * LDV;
       if (warp * 16 < n_rows) {  // a warp whose rows are all padding only helps with the copies
 
       // S = Q K^T : 16 rows x 64 keys per warp
@@ -201,7 +225,7 @@ __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Attn
 #pragma unroll
         for (int d2 = 0; d2 < DTILES / 2; ++d2) {
           uint32_t b[4];
-          ldmatrix_x4_trans(b, vb + (kk * 16 + (lane % 8) + ((lane / 8) % 2) * 8) * LD + d2 * 16 + (lane / 16) * 8);
+          ldmatrix_x4_trans(b, vb + (kk * 16 + (lane % 8) + ((lane / 8) % 2) * 8) * LDV + d2 * 16 + (lane / 16) * 8);
           mma_bf16(o_acc[2 * d2], pa, b[0], b[1]);
           mma_bf16(o_acc[2 * d2 + 1], pa, b[2], b[3]);
         }
@@ -212,6 +236,19 @@ __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Attn
   }
   cp_async_wait<0>();
 
+  if (!SPLIT && p.sink != nullptr) {  // one more term of the denominator (scores are in units of log2(e); the sink is not scaled)
+    const float sk_a = p.sink[kvh * g + min(row_a, n_rows - 1) % g] * 1.4426950408889634f;
+    const float sk_b = p.sink[kvh * g + min(row_b, n_rows - 1) % g] * 1.4426950408889634f;
+    const float mn_a = fmaxf(m_a, sk_a), mn_b = fmaxf(m_b, sk_b);
+    const float al_a = exp2f(m_a - mn_a), al_b = exp2f(m_b - mn_b);
+    l_a = l_a * al_a + exp2f(sk_a - mn_a);
+    l_b = l_b * al_b + exp2f(sk_b - mn_b);
+#pragma unroll
+    for (int d = 0; d < DTILES; ++d) {
+      o_acc[d][0] *= al_a; o_acc[d][1] *= al_a;
+      o_acc[d][2] *= al_b; o_acc[d][3] *= al_b;
+    }
+  }
   // ---- write: rows a and b of this thread, columns 2*(lane%4)+{0,1} of every 8-wide tile
   const float inv_a = l_a > 0.f ? 1.f / l_a : 0.f, inv_b = l_b > 0.f ? 1.f / l_b : 0.f;
 #pragma unroll
@@ -221,10 +258,22 @@ __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Attn
     const int tq = row / g, hg = row % g;
     const float inv = half ? inv_b : inv_a;
     if (!SPLIT) {
-      bf16* dst = p.out + (size_t)(tok_base + tq) * p.ld_out + (size_t)(kvh * g + hg) * HD + 2 * (lane % 4);
+      bf16* dst = p.out + (size_t)(tok_base + tq) * p.ld_out + (size_t)(kvh * g + hg) * HDV + 2 * (lane % 4);
+      const size_t gcol = (size_t)(tok_base + tq) * p.g_width + p.g_off + (size_t)(kvh * g + hg) * HDV + 2 * (lane % 4);
 #pragma unroll
-      for (int d = 0; d < DTILES; ++d)
-        *reinterpret_cast<uint32_t*>(dst + d * 8) = pack_bf16(o_acc[d][2 * half] * inv, o_acc[d][2 * half + 1] * inv);
+      for (int d = 0; d < DTILES; ++d) {
+        float v0 = o_acc[d][2 * half] * inv, v1 = o_acc[d][2 * half + 1] * inv;
+        if (p.gate != nullptr) {  // times sigmoid of the gate's sums, added in index order
+          float g0 = p.gate[gcol + d * 8], g1 = p.gate[gcol + d * 8 + 1];
+          for (int k = 1; k < p.g_parts; ++k) {
+            g0 += p.gate[(size_t)k * p.g_pstride + gcol + d * 8];
+            g1 += p.gate[(size_t)k * p.g_pstride + gcol + d * 8 + 1];
+          }
+          v0 = v0 / (1.0f + expf(-g0));
+          v1 = v1 / (1.0f + expf(-g1));
+        }
+        *reinterpret_cast<uint32_t*>(dst + d * 8) = pack_bf16(v0, v1);
+      }
     } else {
       const size_t slot = ((size_t)split * p.part_stride_tokens + (tok_base + tq)) * p.nq + (kvh * g + hg);
       float* dst = p.part_o + slot * HD + 2 * (lane % 4);
@@ -297,6 +346,19 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
   }
 }
 
+template <int HD, int HDV>
+int launch_plain(const AttnParams& p, int n_seqs, int max_new_tokens, cudaStream_t stream) {
+  const int g = p.nq / p.nkv;
+  const size_t smem = ((size_t)(M_TILE + 2 * N_TILE) * (HD + 8) + (size_t)2 * N_TILE * (HDV + 8)) * sizeof(bf16);
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(paged_attention_mma_kernel<HD, HDV, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return 1;
+  const int tq_cap = M_TILE / g;
+  dim3 grid((max_new_tokens + tq_cap - 1) / tq_cap, n_seqs, p.nkv);
+  launch_kernel(paged_attention_mma_kernel<HD, HDV, false>, grid, THREADS, smem, stream, p);
+  return 0;
+}
+
 template <int HD>
 int launch(const AttnParams& p, int n_seqs, int max_new_tokens, int n_tokens, bool split, cudaStream_t stream) {
   constexpr int LD = HD + 8;
@@ -309,14 +371,14 @@ int launch(const AttnParams& p, int n_seqs, int max_new_tokens, int n_tokens, bo
   const int tq_cap = M_TILE / g;
   dim3 grid((max_new_tokens + tq_cap - 1) / tq_cap, n_seqs, p.nkv * (split ? p.n_splits : 1));
   if (split) {
-    if (!set_attr(paged_attention_mma_kernel<HD, true>, smem)) return 1;
-    launch_kernel(paged_attention_mma_kernel<HD, true>, grid, THREADS, smem, stream, p);
+    if (!set_attr(paged_attention_mma_kernel<HD, HD, true>, smem)) return 1;
+    launch_kernel(paged_attention_mma_kernel<HD, HD, true>, grid, THREADS, smem, stream, p);
     const int items = n_tokens * p.nq;
     launch_kernel(attention_combine_kernel<HD>, (items + 3) / 4, 128, 0, stream, (const float*)p.part_o, (const float*)p.part_ml,
                   p.n_splits, p.part_stride_tokens, p.nq, p.out, p.ld_out, n_tokens);
   } else {
-    if (!set_attr(paged_attention_mma_kernel<HD, false>, smem)) return 1;
-    launch_kernel(paged_attention_mma_kernel<HD, false>, grid, THREADS, smem, stream, p);
+    if (!set_attr(paged_attention_mma_kernel<HD, HD, false>, smem)) return 1;
+    launch_kernel(paged_attention_mma_kernel<HD, HD, false>, grid, THREADS, smem, stream, p);
   }
   return 0;
 }
@@ -358,6 +420,7 @@ extern "C" int llm_paged_attention_mma(const void* q, long long ld_q, const void
   p.seq_start = seq_start; p.seq_ntok = seq_ntok; p.seq_qoff = seq_qoff; p.block_table = block_table;
   p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window; p.scale = scale;
   p.out = (bf16*)out; p.ld_out = ld_out;
+  p.chunk = 0; p.sink = nullptr; p.gate = nullptr; p.g_parts = 0; p.g_pstride = 0; p.g_width = 0; p.g_off = 0;
   p.n_splits = n_splits; p.split_keys = split_keys; p.part_stride_tokens = n_tokens;
   p.part_o = scratch; p.part_ml = scratch ? scratch + (size_t)n_splits * n_tokens * nq * hd : nullptr;
   const bool split = n_splits > 1;
@@ -368,5 +431,45 @@ extern "C" int llm_paged_attention_mma(const void* q, long long ld_q, const void
   else rc = launch<128>(p, n_seqs, max_new_tokens, n_tokens, split, stream);
   LLM_REQUIRE(rc == 0, "attention_mma: cannot raise the shared memory limit");
   LLM_CHECK_LAUNCH("paged_attention_mma");
+  return LLM_OK;
+}
+
+// The same kernel with its options: keys of dk and values of dv numbers a head (each 32, 64 or 128), chunks, a sink per query
+// head, a gate given as float32 partial sums [g_parts, tokens, g_width] read at columns g_off + head * dv + d. No splits: a
+// (request, key/value head, tile of query rows) is one CTA that walks the keys it may see.
+extern "C" int llm_gated_attention_mma_supported(int nq, int nkv, int dk, int dv, long long ld_q, long long ld_out) {
+  if (nkv <= 0 || nq % nkv) return 0;
+  const int g = nq / nkv;
+  const bool sizes = (dk == 32 || dk == 64 || dk == 128) && (dv == 32 || dv == 64 || dv == 128);
+  return sizes && g <= M_TILE && (ld_q % 8) == 0 && (ld_out % 2) == 0;
+}
+
+extern "C" int llm_gated_attention_mma(const void* q, long long ld_q, const void* kcache, const void* vcache, const int* seq_start,
+                                       const int* seq_ntok, const int* seq_qoff, const int* block_table, int max_blocks, void* out,
+                                       long long ld_out, int n_seqs, int max_new_tokens, int nq, int nkv, int dk, int dv, int page_size,
+                                       float scale, int window, int chunk, const float* sink, const float* gate, int g_parts,
+                                       long long g_pstride, int g_width, int g_off, cudaStream_t stream) {
+  if (n_seqs == 0 || max_new_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(llm_gated_attention_mma_supported(nq, nkv, dk, dv, ld_q, ld_out), "gated_attention_mma: geometry not supported (nq=%d nkv=%d dk=%d dv=%d)", nq, nkv, dk, dv);
+  LLM_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0 && chunk >= 0 && max_new_tokens > 0, "gated_attention_mma: bad sizes");
+  LLM_REQUIRE((reinterpret_cast<uintptr_t>(q) & 15u) == 0 && (reinterpret_cast<uintptr_t>(kcache) & 15u) == 0 &&
+              (reinterpret_cast<uintptr_t>(vcache) & 15u) == 0, "gated_attention_mma: q and the caches must be 16-byte aligned");
+  LLM_REQUIRE(gate == nullptr || (g_parts >= 1 && g_off >= 0 && (long long)g_off + (long long)nq * dv <= g_width), "gated_attention_mma: gate columns outside the product");
+  LLM_REQUIRE((long long)n_seqs <= 65535 && nkv <= 65535, "gated_attention_mma: batch too large for the grid");
+  AttnParams p;
+  p.q = (const bf16*)q; p.ld_q = ld_q; p.kcache = (const bf16*)kcache; p.vcache = (const bf16*)vcache;
+  p.seq_start = seq_start; p.seq_ntok = seq_ntok; p.seq_qoff = seq_qoff; p.block_table = block_table;
+  p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window; p.scale = scale;
+  p.out = (bf16*)out; p.ld_out = ld_out;
+  p.chunk = chunk; p.sink = sink; p.gate = gate; p.g_parts = g_parts; p.g_pstride = g_pstride; p.g_width = g_width; p.g_off = g_off;
+  p.n_splits = 1; p.split_keys = 0; p.part_stride_tokens = 0; p.part_o = nullptr; p.part_ml = nullptr;
+  int rc = 1;
+#define LLM_GATED(K, V) if (dk == K && dv == V) rc = launch_plain<K, V>(p, n_seqs, max_new_tokens, stream)
+  LLM_GATED(32, 32); LLM_GATED(32, 64); LLM_GATED(32, 128);
+  LLM_GATED(64, 32); LLM_GATED(64, 64); LLM_GATED(64, 128);
+  LLM_GATED(128, 32); LLM_GATED(128, 64); LLM_GATED(128, 128);
+#undef LLM_GATED
+  LLM_REQUIRE(rc == 0, "gated_attention_mma: cannot raise the shared memory limit");
+  LLM_CHECK_LAUNCH("gated_attention_mma");
   return LLM_OK;
 }

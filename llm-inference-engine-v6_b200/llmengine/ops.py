@@ -80,7 +80,7 @@ class CudaOps:
         self.tma_decode_attention = True  # single decoded tokens: keys and values by TMA where the geometry allows it
         self.fused_decode_attention = True  # ... with the sum of the q|k|v parts, rotation and cache write in the same kernel
         self.latent_tensor_cores = True  # latent attention on mma.sync where the geometry allows it (off: CUDA cores)
-        self.gated_attention_tensor_cores = False  # gated attention on mma.sync where the geometry allows it (off: CUDA cores)
+        self.gated_attention_tensor_cores = True  # gated attention on mma.sync where the geometry allows it (off: CUDA cores)
         self.routed_tensor_cores = True  # per-expert products of a routed feed-forward on mma.sync (off: CUDA cores)
         # Steps of few tokens: products that add their K pieces themselves, with the norm before, the residual sum
         # and SiLU * up folded in (gemm_few_tokens). Off: measured on B200 (batch 8, 2,048-token contexts, 1B layer

@@ -110,8 +110,20 @@ def mixer_harness(dt, spec, page, part):
     return h, c
 
 
+def _one_attention_layer(heads, kv_heads, dim, vdim, chunk, dims):
+    """A configuration of one attention layer, for the head sizes that the tensor-core kernel takes."""
+    from tiny_zulopel import _att
+    return {"architecture": "Zulopel", "vocab": 64, "width": 80, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0}, "max_positions": 256,
+            "layers": [{"type": "attention", "mixer": _att(heads, kv_heads, dim, vdim, dim ** -0.5, dims, 1000.0, chunk), "mlp": None}]}
+
+
+ATTENTION_CASES = [(ZULOPEL_A, 4), (ZULOPEL_B, 0), (ZULOPEL_C, 1), (_one_attention_layer(6, 2, 64, 32, 16, 24), 0),
+                   (_one_attention_layer(8, 1, 128, 128, 0, 128), 0), (_one_attention_layer(2, 2, 32, 128, 7, 0), 0),
+                   (_one_attention_layer(12, 3, 128, 64, 21, 64), 0)]
+
+
 @pytest.mark.parametrize("dt", DTYPES)
-@pytest.mark.parametrize("cfg,i", [(ZULOPEL_A, 4), (ZULOPEL_B, 0), (ZULOPEL_C, 1)], ids=["a4", "b0", "c1"])
+@pytest.mark.parametrize("cfg,i", ATTENTION_CASES, ids=["a4", "b0", "c1", "64x32", "128x128", "32x128", "128x64"])
 @pytest.mark.parametrize("sharp", [False, True])
 def test_gated_attention_alone(dt, cfg, i, sharp):
     """The mixer over a prompt portion, then over single tokens and a second portion that read the first one's cache rows;
