@@ -454,15 +454,16 @@ extern "C" int llm_stream_add(float* h, const float* a, int na, long long sa, co
 // index order; h[r] += ((y / sqrt(mean(y^2) + eps)) * w) * ls  (ls: an optional per-column layer scale); copy[r] (optional) =
 // the new h[r] in the engine dtype, the operand of the products that read the stream next. One block a row, float32.
 namespace {
-template <typename T>
+constexpr int NA_MAX = 8;  // elements of a row that a thread keeps between the two passes
+
+template <typename T, bool KEEP>  // KEEP: dim <= NA_MAX * blockDim, the row's sums stay in registers
 __global__ void norm_add_kernel(float* __restrict__ h, const float* __restrict__ a, int na, size_t sa, const float* __restrict__ b, int nb,
                                 size_t sb, const float* __restrict__ w, const float* __restrict__ ls, float eps, T* __restrict__ copy, int dim) {
   __shared__ float red[33];
   dep_launch();
   dep_wait();
   const size_t base = (size_t)blockIdx.x * dim;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+  auto sum_at = [&](int i) {
     float y = a[base + i];
     for (int p = 1; p < na; ++p) y += a[(size_t)p * sa + base + i];
     if (b) {
@@ -470,23 +471,40 @@ __global__ void norm_add_kernel(float* __restrict__ h, const float* __restrict__
       for (int p = 1; p < nb; ++p) d += b[(size_t)p * sb + base + i];
       y += d;
     }
-    ss += y * y;
+    return y;
+  };
+  float keep[NA_MAX];
+  float ss = 0.f;
+  if (KEEP) {
+#pragma unroll
+    for (int k = 0; k < NA_MAX; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      keep[k] = i < dim ? sum_at(i) : 0.f;
+      ss += keep[k] * keep[k];
+    }
+  } else {
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+      const float y = sum_at(i);
+      ss += y * y;
+    }
   }
   ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
-  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-    float y = a[base + i];
-    for (int p = 1; p < na; ++p) y += a[(size_t)p * sa + base + i];
-    if (b) {
-      float d = b[base + i];
-      for (int p = 1; p < nb; ++p) d += b[(size_t)p * sb + base + i];
-      y += d;
-    }
+  auto finish = [&](int i, float y) {
     float v = y * inv * w[i];
     if (ls) v *= ls[i];
     const float x = h[base + i] + v;
     h[base + i] = x;
     if (copy) copy[base + i] = from_f32<T>(x);
+  };
+  if (KEEP) {
+#pragma unroll
+    for (int k = 0; k < NA_MAX; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      if (i < dim) finish(i, keep[k]);
+    }
+  } else {
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) finish(i, sum_at(i));
   }
 }
 }  // namespace
@@ -496,12 +514,13 @@ extern "C" int llm_norm_add(float* h, const float* a, int na, long long sa, cons
   if (n_rows == 0) return LLM_OK;
   LLM_REQUIRE(n_rows > 0 && dim > 0 && a != nullptr && na >= 1 && (b == nullptr || nb >= 1) && w != nullptr, "norm_add: bad arguments");
   const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
-  if (copy_dtype == LLM_F32)
-    launch_kernel(norm_add_kernel<float>, n_rows, threads, 0, stream, h, a, na, (size_t)sa, b, nb, (size_t)sb, w, ls, eps, (float*)copy, dim);
-  else if (copy_dtype == LLM_BF16)
-    launch_kernel(norm_add_kernel<bf16>, n_rows, threads, 0, stream, h, a, na, (size_t)sa, b, nb, (size_t)sb, w, ls, eps, (bf16*)copy, dim);
-  else
-    LLM_REQUIRE(false, "norm_add: unknown dtype %d", copy_dtype);
+  LLM_REQUIRE(copy_dtype == LLM_F32 || copy_dtype == LLM_BF16, "norm_add: unknown dtype %d", copy_dtype);
+#define LLM_NA(T, KEEP) \
+  launch_kernel(norm_add_kernel<T, KEEP>, n_rows, threads, 0, stream, h, a, na, (size_t)sa, b, nb, (size_t)sb, w, ls, eps, (T*)copy, dim)
+  const bool keep = dim <= NA_MAX * threads;
+  if (copy_dtype == LLM_F32) { if (keep) LLM_NA(float, true); else LLM_NA(float, false); }
+  else { if (keep) LLM_NA(bf16, true); else LLM_NA(bf16, false); }
+#undef LLM_NA
   LLM_CHECK_LAUNCH("norm_add");
   return LLM_OK;
 }

@@ -48,8 +48,8 @@ __global__ void __launch_bounds__(PREP_WARPS * 32)
   const int page = block_table[(size_t)token_seq[tok] * max_blocks + pos / page_size];
   const int in_page = pos % page_size;
   float* buf = sh + (size_t)warp * dk;
-  // query heads 0..H-1, then key heads H..H+G-1: a warp a head
-  for (int head = warp; head < H + G; head += PREP_WARPS) {
+  // query heads 0..H-1, then key heads H..H+G-1: a warp a head; the blocks of a token (blockIdx.y) share its heads and values
+  for (int head = blockIdx.y * PREP_WARPS + warp; head < H + G; head += gridDim.y * PREP_WARPS) {
     const bool is_q = head < H;
     const size_t col0 = is_q ? (size_t)head * dk : (size_t)H * dk + (size_t)(head - H) * dk;
     const float* w = is_q ? wq : wk;
@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(PREP_WARPS * 32)
   // values
   const size_t vcol0 = (size_t)(H + G) * dk;
   const float lam = mix_role == 2 ? *lambda : 0.f;
-  for (int i = threadIdx.x; i < G * dv; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < G * dv; i += gridDim.y * blockDim.x) {
     float v = parts_sum(parts, n_parts, pstride, row + vcol0 + i);
     if (mix_role == 1) v_first[(size_t)tok * G * dv + i] = v;
     else if (mix_role == 2) v = (1.0f - lam) * v + lam * v_first[(size_t)tok * G * dv + i];
@@ -197,8 +197,10 @@ extern "C" int llm_qkv_prep(const float* parts, int n_parts, long long pstride, 
   LLM_REQUIRE(mix_role == 0 || (v_first && (mix_role == 1 || (mix_role == 2 && lambda))), "qkv_prep: value mixing needs its buffer and weight");
   const size_t smem = (size_t)PREP_WARPS * dk * sizeof(float);
   LLM_REQUIRE(smem <= 48 * 1024, "qkv_prep: a head of %d numbers exceeds one block's shared memory", dk);
+  // few tokens: the heads of a token are spread over several blocks, so that the sums of many parts are read side by side
+  dim3 grid(n_tokens, n_tokens >= 512 ? 1 : min(ceil_div(H + G, PREP_WARPS), 8));
 #define LLM_PREP(T)                                                                                                                  \
-  launch_kernel(qkv_prep_kernel<T>, n_tokens, PREP_WARPS * 32, smem, stream, parts, n_parts, (size_t)pstride, width, H, G, dk, dv,    \
+  launch_kernel(qkv_prep_kernel<T>, grid, PREP_WARPS * 32, smem, stream, parts, n_parts, (size_t)pstride, width, H, G, dk, dv,    \
                 rot_dims, wq, wk, eps, cos_t, sin_t, positions, token_seq, block_table, max_blocks, (T*)q_out, ld_q, (T*)kcache,       \
                 (T*)vcache, page_size, mix_role, lambda, v_first)
   if (dtype == LLM_F32) LLM_PREP(float);

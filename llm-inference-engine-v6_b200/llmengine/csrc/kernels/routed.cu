@@ -94,10 +94,25 @@ __global__ void route_grouped_kernel(const T* __restrict__ x, long long ldx, con
   dep_wait();
   const int tok = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const T* xr = x + (size_t)tok * ldx;
+  const bool vec = D % 8 == 0 && sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(xr) & 15u) == 0 && (reinterpret_cast<uintptr_t>(wr) & 15u) == 0;
   for (int e = warp; e < E; e += nw) {
     const T* w = wr + (size_t)e * D;
     float acc = 0.f;
-    for (int k = lane; k < D; k += 32) acc = fmaf(to_f32(xr[k]), to_f32(w[k]), acc);
+    if (vec) {  // bfloat16 rows, 16 bytes a lane a step
+      for (int k = lane * 8; k < D; k += 256) {
+        const uint4 xa = *reinterpret_cast<const uint4*>(xr + k), wa = *reinterpret_cast<const uint4*>(w + k);
+        const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xa);
+        const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wa);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 xf = __bfloat1622float2(xh[i]), wf = __bfloat1622float2(wh[i]);
+          acc = fmaf(xf.x, wf.x, acc);
+          acc = fmaf(xf.y, wf.y, acc);
+        }
+      }
+    } else {
+      for (int k = lane; k < D; k += 32) acc = fmaf(to_f32(xr[k]), to_f32(w[k]), acc);
+    }
     acc = warp_sum(acc);
     if (lane == 0) s[e] = acc;
   }

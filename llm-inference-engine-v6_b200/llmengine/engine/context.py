@@ -82,6 +82,7 @@ class StepContext:
         # what one layer of the step leaves for later layers of the same step, by a name they agree on (the values that a
         # layer with value mixing hands to the layers after it); tensors of the workspace, so their addresses stay fixed
         self.shared: Dict[str, object] = {}
+        self.takes_delta_pairs = False  # set by a block while it runs a feed-forward whose two branches' sums it adds itself
 
 
 class StepBuffers:

@@ -1198,12 +1198,25 @@ class CudaOps:
             _need(skip, "scan.skip", torch.float32)
             assert skip.numel() == C
         lib = self.lib()
+        # a long portion is cut into pieces that run side by side (two passes and a carry between them); short ones and single
+        # decoded tokens are walked in one pass
+        piece = int(lib.llm_selective_scan_piece())
+        pieces, piece_state, piece_sumdt = 0, None, None
+        if batch.max_new_tokens >= self.SCAN_PIECES_FROM:
+            pieces = batch.n_tokens // piece + batch.n_seqs
+            piece_state = batch.ws.get("scan.piece_state", (pieces, C, N), torch.float32)
+            piece_sumdt = batch.ws.get("scan.piece_sumdt", (pieces, C), torch.float32)
         self._check(lib.llm_selective_scan(_ptr(xc), _ptr(dt), _ptr(proj), c_longlong(proj.stride(0)), c_int(b_off), c_int(c_off),
                                            _ptr(zparts), c_int(zparts.shape[0]), c_longlong(zparts.stride(0)), c_int(zparts.shape[2]),
                                            c_int(z_off), _ptr(a_log), _ptr(skip), _ptr(state), _ptr(batch.seq_qoff), _ptr(batch.seq_ntok),
                                            _ptr(batch.seq_slot), c_int(C), c_int(N), _ptr(out), c_int(dtype_code(xc.dtype)),
-                                           c_int(batch.n_seqs), _stream()), lib)
+                                           c_int(batch.n_seqs), c_int(batch.max_new_tokens), c_int(pieces), _ptr(piece_state),
+                                           _ptr(piece_sumdt), _stream()), lib)
+        if pieces:
+            self.launches += 2
         return out
+
+    SCAN_PIECES_FROM = 192  # tokens of the step's longest portion from which the scan runs in pieces
 
     # ------------------------------------------------------------------ sampling
     def sample_scratch_words(self, n_rows: int, vocab: int) -> int:

@@ -81,8 +81,9 @@ class GroupRoutedMLP(FeedForward):
         out = sum_e g_e * Wdown_e (silu(Wgate_e x) * Wup_e x)  +  shared(x)
 
     An expert's gate and up rows are stored in turn ([E, 2 ff, hidden]: row 2 f the gate, row 2 f + 1 its up row), so that the
-    per-expert product has both in one thread's hands and applies silu(gate) * up in its epilogue. Returns the routed sum and
-    the shared expert's product as two sets of partial sums, [2 or more, tokens, hidden], for the next reader to add."""
+    per-expert product has both in one thread's hands and applies silu(gate) * up in its epilogue. Where the caller says that
+    it takes pairs (ctx.takes_delta_pairs: a block that adds two sets of sums in one kernel), the routed sum and the shared
+    expert's partial sums are returned side by side; otherwise they are added here."""
 
     def __init__(self, spec: GroupRoutedMLPSpec, env):
         super().__init__(spec, env)
@@ -153,11 +154,11 @@ class GroupRoutedMLP(FeedForward):
         ctx.residual = None
         b = self.shared.forward(x, ctx)
         ctx.residual = keep
-        b = b if b.dim() == 3 else b.unsqueeze(0)
-        out = ctx.ws.get("routed.delta", (1 + b.shape[0], n, s.hidden), torch.float32)
-        ops.routed_combine(y, out[0], s.top)
-        out[1:].copy_(b)
-        return out
+        out = ctx.ws.get("routed.delta", (n, s.hidden), torch.float32)
+        ops.routed_combine(y, out, s.top)
+        if getattr(ctx, "takes_delta_pairs", False):
+            return out, b  # the caller adds the two sets of sums itself, in this order
+        return ops.stream_add(out, b, n_rows=n)
 
 
 register_part("feed_forward", "routed_mlp", RoutedMLP)

@@ -99,12 +99,12 @@ def test_feed_forward_alone(dt, cfg, i, n):
 
 
 def mixer_harness(dt, spec, page, part):
-    h = Harness(dt, page=page, pages=40)
+    h = Harness(dt, page=page, pages=120)
     c = LayerCache(group=0)
     for need in part.cache_needs():
         if hasattr(need, "head_dim"):
-            c.k = torch.zeros(41, need.num_kv_heads, page, need.head_dim, dtype=dt, device=DEV)
-            c.v = torch.zeros(41, need.num_kv_heads, page, need.value_dim, dtype=dt, device=DEV)
+            c.k = torch.zeros(121, need.num_kv_heads, page, need.head_dim, dtype=dt, device=DEV)
+            c.v = torch.zeros(121, need.num_kv_heads, page, need.value_dim, dtype=dt, device=DEV)
         else:
             c.states[need.name] = torch.zeros((5,) + tuple(need.shape), dtype=need.dtype, device=DEV)
     return h, c
@@ -149,9 +149,10 @@ def test_selective_scan_alone(dt, cfg, i):
     h, cache = mixer_harness(dt, spec, 4, build_part("mixer", spec.mixer, Harness(dt).env))
     part = build_part("mixer", spec.mixer, h.env)
     part.load(dev)
-    x = (2 * torch.randn(90, cfg["width"], generator=torch.Generator().manual_seed(16))).to(dt)
+    x = (2 * torch.randn(420, cfg["width"], generator=torch.Generator().manual_seed(16))).to(dt)
     state = {}
-    for lo, hi in ((0, 1), (1, 3), (3, 4), (4, 70), (70, 71), (71, 73), (73, 90)):
+    # (the portion of 310 tokens runs in pieces side by side, with a carry between two passes)
+    for lo, hi in ((0, 1), (1, 3), (3, 4), (4, 70), (70, 71), (71, 73), (73, 90), (90, 400), (400, 401), (401, 420)):
         ctx = h.ctx([(1, hi - lo, [])])
         got = whole(part.forward(x[lo:hi].to(DEV), ctx, cache)).cpu()
         ref = P.mamba_mixer(x[lo:hi].double(), cpu, f"l{i}.mix.", cfg["layers"][i]["mixer"], state)
@@ -222,6 +223,25 @@ def test_cuts_match_plain_and_one_another(model, cut):
         if dt == torch.float32:  # where the first wrong position is, if any
             bad = np.nonzero(np.abs(got - plain[k]).max(1) > 1e-3 * max(1.0, np.abs(plain[k]).max()))[0]
             assert bad.size == 0, f"{cut}, request {k}: first wrong position {bad[0]} of {len(ids)}"
+
+
+def test_scan_in_pieces_beside_single_tokens(model):
+    """The mixed batches once more with the recurrent layers' scan cut into pieces already for portions of 65 tokens: pieces
+    of unequal requests side by side, single tokens of other requests among them."""
+    dt, eng, reqs, plain, tokens, _, cfg = model
+    if dt == torch.bfloat16 and cfg is ZULOPEL_A:
+        # one expert of five: where rounding flips that choice early in a request, the slow decays of these weights carry the
+        # difference through the rest of it; this configuration's pieces are compared in float32
+        pytest.skip("bfloat16 with a single chosen expert: compared in float32")
+    ops = get_ops()
+    ops.SCAN_PIECES_FROM = 65
+    try:
+        named = {f"pieces.{k}": v for k, v in reqs.items()}
+        rows = replay(eng, trace_mixed(named, tokens, seed=9, sizes=(1, 2, 70, 130, 66)))
+    finally:
+        del ops.SCAN_PIECES_FROM
+    for k, ids in reqs.items():
+        rows_close(np.stack([rows[(f"pieces.{k}", p)] for p in range(len(ids))]), plain[k], dt, f"request {k}")
 
 
 def test_keys_at_page_borders_chunk_edges_and_first_tokens(model):
