@@ -1182,11 +1182,12 @@ class CudaOps:
 
     def selective_scan(self, xc: torch.Tensor, dt: torch.Tensor, proj: torch.Tensor, b_off: int, c_off: int, state_size: int,
                        zparts: torch.Tensor, z_off: int, a_log: torch.Tensor, skip: Optional[torch.Tensor], state: torch.Tensor, batch,
-                       out: torch.Tensor) -> torch.Tensor:
+                       out: torch.Tensor, dt_bias: Optional[torch.Tensor] = None, dt_raw: bool = False) -> torch.Tensor:
         """Token after token of every request: S[c, n] <- exp(dt[t, c] * A[c, n]) * S[c, n] + dt[t, c] * xc[t, c] * B[t, n],
         y[t, c] = sum_n S[c, n] * C[t, n] + skip[c] * xc[t, c], out[t, c] = y * silu(z[t, c]); A = -exp(a_log) [channels, N];
         B, C = columns b_off.., c_off.. of the float32 rows proj; z = columns z_off.. of the float32 sums zparts [p, n, width];
-        state [slots, channels, N] float32, read from and written to the request's slot."""
+        state [slots, channels, N] float32, read from and written to the request's slot. dt_raw: dt holds the sums of the step-size
+        product, and the kernel applies softplus(dt + dt_bias) itself."""
         _need(xc, "scan.x"); _need(dt, "scan.dt", torch.float32); _need(proj, "scan.proj", torch.float32)
         _need(zparts, "scan.z", torch.float32); _need(a_log, "scan.a_log", torch.float32); _need(state, "scan.state", torch.float32)
         _need(out, "scan.out", xc.dtype)
@@ -1211,7 +1212,7 @@ class CudaOps:
                                            c_int(z_off), _ptr(a_log), _ptr(skip), _ptr(state), _ptr(batch.seq_qoff), _ptr(batch.seq_ntok),
                                            _ptr(batch.seq_slot), c_int(C), c_int(N), _ptr(out), c_int(dtype_code(xc.dtype)),
                                            c_int(batch.n_seqs), c_int(batch.max_new_tokens), c_int(pieces), _ptr(piece_state),
-                                           _ptr(piece_sumdt), _stream()), lib)
+                                           _ptr(piece_sumdt), _ptr(dt_bias), c_int(1 if dt_raw else 0), _stream()), lib)
         if pieces:
             self.launches += 2
         return out

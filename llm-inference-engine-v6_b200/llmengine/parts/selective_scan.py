@@ -8,8 +8,10 @@ With h the mixer's input, per token (C channels, N state numbers a channel, K ta
     y_c = sum_n S[c, n] Cm_n + skip_c x_c;   out = W_o (y * silu(z))
 What a request keeps between steps is of fixed size and lives in its state slot: S (float32 [C, N]) and the last K - 1
 inputs of the convolution (float32 [K - 1, C]); both start at zero. Step sizes, decays, B, Cm and the state are float32
-in both engine precisions (the W_x product is written out in float32 and the step-size map runs on CUDA cores from it);
-the convolution's result is rounded to the engine precision once, as the operand of W_x.
+in both engine precisions. With up to 8 tokens, and always in the 32-bit engine, the W_x product is written out in float32 and the
+step-size map runs on CUDA cores from it; with more tokens in bfloat16 the low-rank rows are a product of their own, rounded to
+bfloat16 as the operand of the step-size map on the tensor cores (a projection, like W_x itself), whose float32 sums the scan
+turns into step sizes. The convolution's result is rounded to the engine precision once, as the operand of W_x.
 """
 from __future__ import annotations
 
@@ -48,6 +50,11 @@ class SelectiveScan(Mixer):
         s = self.spec
         self.w_in, self.w_conv, self.conv_bias = tensors[s.in_weight], tensors[s.conv_weight], tensors[s.conv_bias]
         self.w_x = tensors[s.x_weight]
+        # for steps of many tokens in bfloat16: the low-rank rows and [B | C] as products of their own, so that the low-rank rows
+        # come out in bfloat16 as the operand of the step-size product on the tensor cores
+        self.w_x_low = self.w_x[:s.dt_rank].contiguous()
+        self.w_x_bc = self.w_x[s.dt_rank:].contiguous()
+        self.w_dt = tensors[s.dt_weight]
         self.w_dt_t = tensors[s.dt_weight].t().contiguous()  # [rank, channels]: neighbouring channels read neighbouring words
         self.dt_bias, self.a_log, self.skip, self.w_o = tensors[s.dt_bias], tensors[s.a_log], tensors[s.skip], tensors[s.o_weight]
 
@@ -63,12 +70,23 @@ class SelectiveScan(Mixer):
             ops.gemm(x[:n], self.w_in, xz[0])
         xc = ctx.ws.get("scan.xc", (n, C), dt)
         ops.conv_silu(xz, 0, C, self.w_conv, self.conv_bias, cache.states["conv"], ctx, xc)
-        proj = ctx.ws.get("scan.proj", (n, R + 2 * N), torch.float32)
-        ops.gemm(xc, self.w_x, proj, ctx.ws)
         step = ctx.ws.get("scan.dt", (n, C), torch.float32)
-        ops.dt_softplus(proj, R, self.w_dt_t, self.dt_bias, step, n)
         y = ctx.ws.get("scan.y", (n, C), dt)
-        ops.selective_scan(xc, step, proj, R, R + N, N, xz, C, self.a_log, self.skip, cache.states["scan"], ctx, y)
+        if dt == torch.bfloat16 and n > 8 and R % 8 == 0 and C % 8 == 0:
+            # more than a handful of tokens: the step-size map is a tensor-core product of the low-rank rows (rounded to bfloat16 as its operand);
+            # bias and softplus are applied where the scan reads the sums
+            low = ctx.ws.get("scan.low", (n, R), dt)
+            ops.gemm(xc, self.w_x_low, low, ctx.ws)
+            proj = ctx.ws.get("scan.proj", (n, 2 * N), torch.float32)
+            ops.gemm(xc, self.w_x_bc, proj, ctx.ws)
+            ops.gemm(low, self.w_dt, step, ctx.ws)
+            ops.selective_scan(xc, step, proj, 0, N, N, xz, C, self.a_log, self.skip, cache.states["scan"], ctx, y,
+                               dt_bias=self.dt_bias, dt_raw=True)
+        else:
+            proj = ctx.ws.get("scan.proj", (n, R + 2 * N), torch.float32)
+            ops.gemm(xc, self.w_x, proj, ctx.ws)
+            ops.dt_softplus(proj, R, self.w_dt_t, self.dt_bias, step, n)
+            ops.selective_scan(xc, step, proj, R, R + N, N, xz, C, self.a_log, self.skip, cache.states["scan"], ctx, y)
         return add_into_stream_or_partials(ops, y, self.w_o, ctx, False, "scan.delta")
 
 
