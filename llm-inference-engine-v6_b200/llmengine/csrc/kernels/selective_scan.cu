@@ -46,24 +46,27 @@ template <typename T>
 __global__ void conv_silu_kernel(const float* __restrict__ parts, int n_parts, size_t pstride, int width, int x_off, int C, int K,
                                  const T* __restrict__ w, const float* __restrict__ bias, const float* __restrict__ conv_state,
                                  const int* __restrict__ token_seq, const int* __restrict__ seq_qoff, const int* __restrict__ seq_slot,
-                                 T* __restrict__ out, size_t total) {
+                                 T* __restrict__ out, int n_tokens) {
   dep_launch();
   dep_wait();
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= total) return;
-  const int tok = (int)(i / C), c = (int)(i - (size_t)tok * C);
-  const int seq = token_seq[tok];
-  const int first = seq_qoff[seq];
-  const float* st = conv_state + (size_t)seq_slot[seq] * (K - 1) * C;
-  float acc = bias ? bias[c] : 0.f;
-  for (int j = 0; j < K; ++j) {
-    const int src = tok - (K - 1) + j;  // flat row of the tap's input, if it is part of this step
-    float v;
-    if (src >= first) v = parts_sum(parts, n_parts, pstride, (size_t)src * width + x_off + c);
-    else v = st[(size_t)((K - 1) + (src - first)) * C + c];  // src - first in [-(K-1), -1]
-    acc = fmaf(to_f32(w[(size_t)c * K + j]), v, acc);
+  // a block: one token (or, beyond the grid's height, every gridDim.y-th), 256 channels; no division on the way to an index
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  for (int tok = blockIdx.y; tok < n_tokens; tok += gridDim.y) {
+    const size_t i = (size_t)tok * C + c;
+    const int seq = token_seq[tok];
+    const int first = seq_qoff[seq];
+    const float* st = conv_state + (size_t)seq_slot[seq] * (K - 1) * C;
+    float acc = bias ? bias[c] : 0.f;
+    for (int j = 0; j < K; ++j) {
+      const int src = tok - (K - 1) + j;  // flat row of the tap's input, if it is part of this step
+      float v;
+      if (src >= first) v = parts_sum(parts, n_parts, pstride, (size_t)src * width + x_off + c);
+      else v = st[(size_t)((K - 1) + (src - first)) * C + c];  // src - first in [-(K-1), -1]
+      acc = fmaf(to_f32(w[(size_t)c * K + j]), v, acc);
+    }
+    out[i] = from_f32<T>(silu_f(acc));
   }
-  out[i] = from_f32<T>(silu_f(acc));
 }
 
 __global__ void conv_state_kernel(const float* __restrict__ parts, int n_parts, size_t pstride, int width, int x_off, int C, int K,
@@ -331,11 +334,21 @@ __global__ void scan_carry_kernel(const float* __restrict__ a_log, float* __rest
   const float A = -expf(a_log[cn]);
   float* slot = state + (size_t)seq_slot[seq] * per_seq + cn;
   float S = *slot;
-  for (int j = 0; j < pieces; ++j) {
-    float* ps = piece_state + (base + j) * per_seq + cn;
-    const float local = *ps, sd = piece_sumdt[(base + j) * C + c];
-    *ps = S;
-    S += fmaf(expm1f(A * sd), S, local);  // (once a piece: the library's expm1f)
+  for (int j0 = 0; j0 < pieces; j0 += 8) {  // eight pieces' loads on their way at a time; the carry itself goes piece by piece
+    float local[8], sd[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const bool in = j0 + u < pieces;
+      local[u] = in ? piece_state[(base + j0 + u) * per_seq + cn] : 0.f;
+      sd[u] = in ? piece_sumdt[(base + j0 + u) * C + c] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (j0 + u < pieces) {
+        piece_state[(base + j0 + u) * per_seq + cn] = S;
+        S += fmaf(expm1f(A * sd[u]), S, local[u]);  // (once a piece: the library's expm1f)
+      }
+    }
   }
   *slot = S;
 }
@@ -348,13 +361,13 @@ extern "C" int llm_conv_silu(const float* parts, int n_parts, long long pstride,
   if (n_tokens == 0) return LLM_OK;
   LLM_REQUIRE(n_tokens > 0 && n_seqs > 0 && n_parts >= 1 && C > 0 && K >= 1 && K <= MAX_TAPS, "conv_silu: bad sizes (taps %d, at most %d)", K, MAX_TAPS);
   LLM_REQUIRE(x_off >= 0 && x_off + C <= width, "conv_silu: columns outside the product");
-  const size_t total = (size_t)n_tokens * C;
+  dim3 grid(ceil_div(C, 256), n_tokens < 65535 ? n_tokens : 65535);
   if (dtype == LLM_F32)
-    launch_kernel(conv_silu_kernel<float>, ceil_div((long long)total, 256), 256, 0, stream, parts, n_parts, (size_t)pstride, width, x_off, C, K,
-                  (const float*)w, bias, (const float*)conv_state, token_seq, seq_qoff, seq_slot, (float*)out, total);
+    launch_kernel(conv_silu_kernel<float>, grid, 256, 0, stream, parts, n_parts, (size_t)pstride, width, x_off, C, K,
+                  (const float*)w, bias, (const float*)conv_state, token_seq, seq_qoff, seq_slot, (float*)out, n_tokens);
   else if (dtype == LLM_BF16)
-    launch_kernel(conv_silu_kernel<bf16>, ceil_div((long long)total, 256), 256, 0, stream, parts, n_parts, (size_t)pstride, width, x_off, C, K,
-                  (const bf16*)w, bias, (const float*)conv_state, token_seq, seq_qoff, seq_slot, (bf16*)out, total);
+    launch_kernel(conv_silu_kernel<bf16>, grid, 256, 0, stream, parts, n_parts, (size_t)pstride, width, x_off, C, K,
+                  (const bf16*)w, bias, (const float*)conv_state, token_seq, seq_qoff, seq_slot, (bf16*)out, n_tokens);
   else
     LLM_REQUIRE(false, "conv_silu: unknown dtype %d", dtype);
   LLM_CHECK_LAUNCH("conv_silu");
