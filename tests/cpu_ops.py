@@ -13,9 +13,9 @@ import torch
 
 
 class CpuOps:
-    def embed(self, table, ids, out):
+    def embed(self, table, ids, out, scale=1.0):
         n = out.shape[0]
-        out.copy_(table[ids[:n].long()].float())
+        out.copy_(table[ids[:n].long()].float() * scale)
         return out
 
     def rmsnorm(self, h, weight, eps, out, delta=None, rows=None, n_rows=None, write_back=True):
@@ -174,6 +174,22 @@ class CpuOps:
         idx.copy_(order.to(torch.int32))
         share.copy_(torch.softmax(torch.gather(z, 1, order), dim=-1))
 
+    def route_grouped(self, x, w, correction, top, groups, keep, norm_eps, idx, share):
+        s = torch.softmax(x.float() @ w.float().t(), dim=-1)
+        choice = s + correction if correction is not None else s.clone()
+        E = s.shape[1]
+        per = E // groups
+        if keep < groups:
+            best = choice.view(-1, groups, per).max(-1).values
+            kept = torch.argsort(best, dim=-1, descending=True, stable=True)[:, :keep]
+            mask = torch.zeros(s.shape[0], groups, dtype=torch.bool)
+            mask.scatter_(1, kept, True)
+            choice = torch.where(mask.repeat_interleave(per, dim=1), choice, torch.full_like(choice, float("-inf")))
+        order = torch.argsort(choice, dim=-1, descending=True, stable=True)[:, :top]
+        picked = torch.gather(s, 1, order)
+        idx.copy_(order.to(torch.int32))
+        share.copy_(picked / (picked.sum(-1, keepdim=True) + norm_eps))
+
     def routed_tile_rows(self, n_tokens=0, dtype=None, inner=(), per_expert=0.0):
         return 4
 
@@ -200,7 +216,12 @@ class CpuOps:
                 if p < 0:
                     continue
                 v = w[e].float() @ a[p // a_div].float()
-                v = 0.5 * v * (1.0 + torch.erf(v / 2.0 ** 0.5)) if epilogue == "gelu" else v * share[p]
+                if epilogue == "gelu":
+                    v = 0.5 * v * (1.0 + torch.erf(v / 2.0 ** 0.5))
+                elif epilogue == "share":
+                    v = v * share[p]
+                else:  # "silu_pairs": rows 2 f and 2 f + 1 are a gate and its up row
+                    v = torch.nn.functional.silu(v[0::2]) * v[1::2]
                 out[p] = v.to(out.dtype)
         return out
 
@@ -232,6 +253,109 @@ class CpuOps:
                 vcache[page, :, pos % ps, :] = v.to(vcache.dtype)
             else:
                 qkv[t, nq * hd:(nq + nkv) * hd] = k.reshape(-1).to(qkv.dtype)
+
+    # ------------------------------------------------------------------ norms on the outputs, gated attention, selective scan
+    def norm_add(self, h, a, b, weight, layer_scale, eps, copy=None, n_rows=None):
+        n = h.shape[0] if n_rows is None else n_rows
+        y = (a if a.dim() == 2 else a.sum(0))[:n].clone()
+        if b is not None:
+            y = y + (b if b.dim() == 2 else b.sum(0))[:n]
+        v = y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps) * weight
+        h[:n] += v * layer_scale if layer_scale is not None else v
+        if copy is not None:
+            copy[:n] = h[:n].to(copy.dtype)
+        return h
+
+    def qkv_prep(self, parts, heads, kv_heads, dk, dv, q_norm, k_norm, eps, cos, sin, batch, block_table, q_out, kcache, vcache,
+                 mix_role=0, mix_weight=None, v_first=None):
+        src = parts.sum(0)
+        half = 0 if cos is None else cos.shape[1]
+        for t in range(batch.n_tokens):
+            pos = int(batch.positions[t])
+            row = src[t].float()
+            q = row[:heads * dk].view(heads, dk).clone()
+            k = row[heads * dk:(heads + kv_heads) * dk].view(kv_heads, dk).clone()
+            v = row[(heads + kv_heads) * dk:(heads + kv_heads) * dk + kv_heads * dv].clone()
+            for x, w in ((q, q_norm), (k, k_norm)):
+                if w is not None:
+                    x.copy_(x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w)
+                if half:
+                    a, b = x[:, :half].clone(), x[:, half:2 * half].clone()
+                    x[:, :half] = a * cos[pos] - b * sin[pos]
+                    x[:, half:2 * half] = b * cos[pos] + a * sin[pos]
+            if mix_role == 1:
+                v_first[t] = v
+            elif mix_role == 2:
+                v = (1.0 - mix_weight) * v + mix_weight * v_first[t]
+            q_out[t] = q.reshape(-1).to(q_out.dtype)
+            if kcache is not None:
+                ps = kcache.shape[2]
+                page = int(block_table[int(batch.token_seq[t]), pos // ps])
+                assert page >= 0, "write into a page that was given back"
+                kcache[page, :, pos % ps, :] = k.to(kcache.dtype)
+                vcache[page, :, pos % ps, :] = v.view(kv_heads, dv).to(vcache.dtype)
+
+    def gated_attention(self, q, kcache, vcache, batch, block_table, out, nq, nkv, dk, dv, scale, window=0, chunk=0, sink=None,
+                        gate=None, gate_off=0):
+        ps, g = kcache.shape[2], nq // nkv
+        gates = gate.sum(0) if gate is not None else None
+        for t in range(batch.n_tokens):
+            pos = int(batch.positions[t])
+            lo = max(0, pos - window + 1) if window > 0 else 0
+            if chunk > 0:
+                lo = max(lo, (pos // chunk) * chunk)
+            idx = torch.arange(lo, pos + 1)
+            pages = block_table[int(batch.token_seq[t])][(idx // ps).long()].long()
+            assert (pages >= 0).all(), "read from a page that was given back"
+            K = kcache[pages, :, (idx % ps).long(), :].float()
+            V = vcache[pages, :, (idx % ps).long(), :].float()
+            qt = q[t].float().view(nq, dk)
+            for h in range(nq):
+                s = (K[:, h // g, :] @ qt[h]) * scale
+                if sink is not None:
+                    p = torch.softmax(torch.cat([s, sink[h:h + 1]]), dim=0)[:-1]
+                else:
+                    p = torch.softmax(s, dim=0)
+                o = p @ V[:, h // g, :]
+                if gates is not None:
+                    o = o * torch.sigmoid(gates[t, gate_off + h * dv:gate_off + (h + 1) * dv])
+                out[t, h * dv:(h + 1) * dv] = o.to(out.dtype)
+        return out
+
+    def conv_silu(self, parts, x_off, channels, weight, bias, conv_state, batch, out):
+        x = parts.sum(0)[:, x_off:x_off + channels]
+        K = weight.shape[1]
+        for s in range(batch.n_seqs):
+            first, n, slot = int(batch.seq_qoff[s]), int(batch.seq_ntok[s]), int(batch.seq_slot[s])
+            padded = torch.cat([conv_state[slot], x[first:first + n]], dim=0)
+            for t in range(n):
+                acc = (bias if bias is not None else 0) + (weight.float().t() * padded[t:t + K]).sum(0)
+                out[first + t] = torch.nn.functional.silu(acc).to(out.dtype)
+            if K > 1:
+                conv_state[slot] = padded[padded.shape[0] - (K - 1):]
+        return out
+
+    def dt_softplus(self, proj, rank, weight_t, bias, out, n_tokens):
+        z = proj[:n_tokens, :rank] @ weight_t.float()
+        out[:n_tokens] = torch.nn.functional.softplus(z + bias if bias is not None else z)
+        return out
+
+    def selective_scan(self, xc, dt, proj, b_off, c_off, state_size, zparts, z_off, a_log, skip, state, batch, out,
+                       dt_bias=None, dt_raw=False):
+        A = -torch.exp(a_log)
+        C, N = a_log.shape
+        z = zparts.sum(0)[:, z_off:z_off + C]
+        for s in range(batch.n_seqs):
+            first, n, slot = int(batch.seq_qoff[s]), int(batch.seq_ntok[s]), int(batch.seq_slot[s])
+            S = state[slot]
+            for t in range(first, first + n):
+                d = torch.nn.functional.softplus(dt[t] + dt_bias) if dt_raw else dt[t]
+                x = xc[t].float()
+                S = torch.exp(d[:, None] * A) * S + (d * x)[:, None] * proj[t, b_off:b_off + N][None, :]
+                y = S @ proj[t, c_off:c_off + N] + (skip * x if skip is not None else 0)
+                out[t] = (y * torch.nn.functional.silu(z[t])).to(out.dtype)
+            state[slot] = S
+        return out
 
     def decode_attention_fusable(self, batch, kcache, nq, nkv, hd, out):
         return False

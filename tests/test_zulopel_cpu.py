@@ -16,6 +16,8 @@ from llmengine.config.zulopel import ZulopelConfig
 from llmengine.models.zulopel import describe_zulopel
 from llmengine.parts.position import ramp_frequencies
 from llmengine.weights.random_init import model_tensor_needs
+from cpu_ops import CpuOps
+from tiny import random_ids
 from tiny_zulopel import ZULOPEL, ZULOPEL_A, ZULOPEL_B, ZULOPEL_C, make_tensors, write_model
 
 
@@ -128,3 +130,58 @@ def test_plain_router_rules():
     assert chosen == [6, 7] and np.allclose(w.numpy(), np.array([0.12, 0.08]) / 0.20)
     chosen, w = P.route(z, corr - 1.0, 2, 4, 1)  # every choice score below zero
     assert chosen == [6, 7]
+
+
+# ---------------------------------------------------------------------------------------------- the engine's host side
+@pytest.fixture(scope="module", params=["za", "zc"])
+def cpu_engine(request, tmp_path_factory):
+    """The engine on the test double of the kernels: batch building, block tables, state slots, the wiring of the parts."""
+    cfg, page = ZULOPEL[request.param]
+    d = write_model(str(tmp_path_factory.mktemp("zulopel_" + request.param)), cfg, torch.float32, sharp=True)
+    eng = llmengine.Engine(d, "fp32", device="cpu", ops=CpuOps(), block_size=page, num_blocks=40)
+    eng.configure_cache(num_blocks=40, block_size=page, num_slots=3)
+    return eng, P.read_model(d), cfg
+
+
+def test_engine_on_the_test_double_matches_plain(cpu_engine):
+    eng, (pc, pw), cfg = cpu_engine
+    a, b = random_ids(37, cfg["vocab"], 1), random_ids(11, cfg["vocab"], 2)
+    want = {k: P.forward(pc, pw, ids).numpy() for k, ids in (("a", a), ("b", b))}
+    got = eng.run_step([(1, a, list(range(len(a))))], end=[1]).numpy()
+    assert np.abs(got - want["a"]).max() < 2e-4
+    # portions beside single tokens of another request; pages and state slots are given back and used again
+    rows = {}
+    steps = [([(2, a[:9], [8]), (3, b[:10], [9])], []), ([(2, a[9:11], [0, 1]), (3, b[10:], [0])], [3]),
+             ([(2, a[11:36], [24]), (4, b[:3], [2])], []), ([(2, a[36:], [0]), (4, b[3:], [7])], [2, 4])]
+    at = {2: 0, 3: 0, 4: 0}
+    for batch, end in steps:
+        lg = eng.run_step(batch, end=end).numpy().copy()  # the logits tensor is scratch of the engine
+        i = 0
+        for rid, toks, w in batch:
+            for k in w:
+                rows[(rid, at[rid] + k)] = lg[i]
+                i += 1
+            at[rid] += len(toks)
+    for (rid, pos), row in rows.items():
+        ref = want["a"] if rid == 2 else want["b"]
+        assert np.abs(row - ref[pos]).max() < 2e-4, (rid, pos)
+    assert eng.cm.num_requests == 0
+
+
+def test_generation_through_the_scheduler_matches_plain(cpu_engine):
+    eng, (pc, pw), cfg = cpu_engine
+    prompt = random_ids(9, cfg["vocab"], 3)
+    out, reason = eng.generate(prompt, 7)
+    assert reason == "length" and out == P.generate(pc, pw, prompt, 7)
+
+
+def test_command_line_random_weights_mode(tmp_path):
+    from test_cli import run_cli
+    cfg = tmp_path / "c.json"
+    cfg.write_text(json.dumps(ZULOPEL_B))
+    out = tmp_path / "model"
+    r = run_cli("--random-weights", str(out), "--config", str(cfg), "--seed", "4", "--dtype", "bf16")
+    assert r.returncode == 0, r.stderr
+    arch, parsed = config_from_dir(str(out))
+    assert arch.name == "Zulopel" and parsed == ZulopelConfig.from_dict(ZULOPEL_B)
+    assert set(P.read_safetensors(str(out / "model.safetensors"))) >= {"embed", "head", "l0.mix.sink", "l1.mix.A_log", "l2.mlp.e15.down", "l0.mlp.shared.up"}
