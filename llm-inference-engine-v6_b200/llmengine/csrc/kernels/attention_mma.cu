@@ -68,9 +68,10 @@ __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Attn
   int lo = (p.window > 0) ? max(0, pos0 - p.window + 1) : 0;  // oldest key any row reads
   if (p.chunk > 0) lo = max(lo, (pos0 / p.chunk) * p.chunk);  // (the first token's chunk begins before the others')
   int hi = pos_last;                                          // newest key any row reads
-  if (SPLIT) {
-    lo = max(lo, split * p.split_keys);
-    hi = min(hi, (split + 1) * p.split_keys - 1);
+  if (SPLIT) {  // (single tokens: with chunks the splits count from the start of the token's chunk)
+    const int base = p.chunk > 0 ? (pos0 / p.chunk) * p.chunk : 0;
+    lo = max(lo, base + split * p.split_keys);
+    hi = min(hi, base + (split + 1) * p.split_keys - 1);
   }
   const int* table = p.block_table + (size_t)seq * p.max_blocks;
   const size_t head_stride = (size_t)p.page_size * HD, head_stride_v = (size_t)p.page_size * HDV;
@@ -276,7 +277,7 @@ __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Attn
       }
     } else {
       const size_t slot = ((size_t)split * p.part_stride_tokens + (tok_base + tq)) * p.nq + (kvh * g + hg);
-      float* dst = p.part_o + slot * HD + 2 * (lane % 4);
+      float* dst = p.part_o + slot * HDV + 2 * (lane % 4);
 #pragma unroll
       for (int d = 0; d < DTILES; ++d) {
         dst[d * 8] = o_acc[d][2 * half] * inv;
@@ -291,11 +292,13 @@ __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Attn
 }
 
 // Merges the splits of every (token, head) in index order: out = sum_s w_s o_s / sum_s w_s,
-// w_s = l_s * 2^(m_s - max m).
+// w_s = l_s * 2^(m_s - max m). With a sink, exp(sink[head]) is one more term below the line (the maximum takes it in);
+// with a gate (float32 partial sums), the result is multiplied by its sigmoid before it is rounded.
 template <int HD>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int n_splits,
                                          long long part_stride_tokens, int nq, bf16* __restrict__ out, long long ld_out,
-                                         int n_tokens) {
+                                         int n_tokens, const float* __restrict__ sink, const float* __restrict__ gate, int g_parts,
+                                         long long g_pstride, int g_width, int g_off) {
   dep_launch();
   dep_wait();
   const int item = blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
@@ -307,6 +310,8 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
   float mx = -INFINITY;
   for (int s = lane; s < n_splits; s += 32) mx = fmaxf(mx, part_ml[(slot0 + s * split_stride) * 2]);
   mx = warp_max(mx);
+  const float sk = sink ? sink[head] * 1.4426950408889634f : -INFINITY;  // (the splits' maxima are in units of log2(e))
+  mx = fmaxf(mx, sk);
   constexpr int R = (HD + 31) / 32;
   float acc[R];
 #pragma unroll
@@ -338,11 +343,21 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
       }
     }
   }
+  if (sink) den += exp2f(sk - mx);
   const float inv = den > 0.f ? 1.f / den : 0.f;
 #pragma unroll
   for (int i = 0; i < R; ++i) {
     const int d = lane + 32 * i;
-    if (d < HD) out[(size_t)tok * ld_out + (size_t)head * HD + d] = __float2bfloat16_rn(acc[i] * inv);
+    if (d < HD) {
+      float v = acc[i] * inv;
+      if (gate) {
+        const size_t col = (size_t)tok * g_width + g_off + (size_t)head * HD + d;
+        float g = gate[col];
+        for (int k = 1; k < g_parts; ++k) g += gate[(size_t)k * g_pstride + col];
+        v = v / (1.0f + expf(-g));
+      }
+      out[(size_t)tok * ld_out + (size_t)head * HD + d] = __float2bfloat16_rn(v);
+    }
   }
 }
 
@@ -375,7 +390,8 @@ int launch(const AttnParams& p, int n_seqs, int max_new_tokens, int n_tokens, bo
     launch_kernel(paged_attention_mma_kernel<HD, HD, true>, grid, THREADS, smem, stream, p);
     const int items = n_tokens * p.nq;
     launch_kernel(attention_combine_kernel<HD>, (items + 3) / 4, 128, 0, stream, (const float*)p.part_o, (const float*)p.part_ml,
-                  p.n_splits, p.part_stride_tokens, p.nq, p.out, p.ld_out, n_tokens);
+                  p.n_splits, p.part_stride_tokens, p.nq, p.out, p.ld_out, n_tokens, p.sink, p.gate, p.g_parts, p.g_pstride, p.g_width,
+                  p.g_off);
   } else {
     if (!set_attr(paged_attention_mma_kernel<HD, HD, false>, smem)) return 1;
     launch_kernel(paged_attention_mma_kernel<HD, HD, false>, grid, THREADS, smem, stream, p);
@@ -435,8 +451,10 @@ extern "C" int llm_paged_attention_mma(const void* q, long long ld_q, const void
 }
 
 // The same kernel with its options: keys of dk and values of dv numbers a head (each 32, 64 or 128), chunks, a sink per query
-// head, a gate given as float32 partial sums [g_parts, tokens, g_width] read at columns g_off + head * dv + d. No splits: a
-// (request, key/value head, tile of query rows) is one CTA that walks the keys it may see.
+// head, a gate given as float32 partial sums [g_parts, tokens, g_width] read at columns g_off + head * dv + d. A (request,
+// key/value head, tile of query rows) is one CTA that walks the keys it may see; steps of single tokens with dk == dv may cut
+// the key range into n_splits pieces of split_keys keys (scratch: llm_attention_mma_scratch_floats), counted from the start of
+// the token's chunk, with sink and gate applied where the pieces are merged.
 extern "C" int llm_gated_attention_mma_supported(int nq, int nkv, int dk, int dv, long long ld_q, long long ld_out) {
   if (nkv <= 0 || nq % nkv) return 0;
   const int g = nq / nkv;
@@ -448,8 +466,12 @@ extern "C" int llm_gated_attention_mma(const void* q, long long ld_q, const void
                                        const int* seq_ntok, const int* seq_qoff, const int* block_table, int max_blocks, void* out,
                                        long long ld_out, int n_seqs, int max_new_tokens, int nq, int nkv, int dk, int dv, int page_size,
                                        float scale, int window, int chunk, const float* sink, const float* gate, int g_parts,
-                                       long long g_pstride, int g_width, int g_off, cudaStream_t stream) {
+                                       long long g_pstride, int g_width, int g_off, int n_tokens, int n_splits, int split_keys,
+                                       float* scratch, cudaStream_t stream) {
   if (n_seqs == 0 || max_new_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(n_splits >= 1 && (n_splits == 1 || (dk == dv && max_new_tokens == 1 && split_keys > 0 && split_keys % N_TILE == 0 && scratch != nullptr)),
+              "gated_attention_mma: splits are for single tokens with keys and values of one size, split_keys %% 64 == 0, and need scratch");
+  LLM_REQUIRE((long long)nkv * n_splits <= 65535, "gated_attention_mma: too many splits for the grid");
   LLM_REQUIRE(llm_gated_attention_mma_supported(nq, nkv, dk, dv, ld_q, ld_out), "gated_attention_mma: geometry not supported (nq=%d nkv=%d dk=%d dv=%d)", nq, nkv, dk, dv);
   LLM_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0 && chunk >= 0 && max_new_tokens > 0, "gated_attention_mma: bad sizes");
   LLM_REQUIRE((reinterpret_cast<uintptr_t>(q) & 15u) == 0 && (reinterpret_cast<uintptr_t>(kcache) & 15u) == 0 &&
@@ -462,8 +484,17 @@ extern "C" int llm_gated_attention_mma(const void* q, long long ld_q, const void
   p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window; p.scale = scale;
   p.out = (bf16*)out; p.ld_out = ld_out;
   p.chunk = chunk; p.sink = sink; p.gate = gate; p.g_parts = g_parts; p.g_pstride = g_pstride; p.g_width = g_width; p.g_off = g_off;
-  p.n_splits = 1; p.split_keys = 0; p.part_stride_tokens = 0; p.part_o = nullptr; p.part_ml = nullptr;
+  p.n_splits = n_splits; p.split_keys = split_keys; p.part_stride_tokens = n_tokens;
+  p.part_o = scratch; p.part_ml = scratch ? scratch + (size_t)n_splits * n_tokens * nq * dv : nullptr;
   int rc = 1;
+  if (n_splits > 1) {  // the key range of every (request, key/value head) in pieces side by side, merged by a second kernel
+    if (dk == 32) rc = launch<32>(p, n_seqs, max_new_tokens, n_tokens, true, stream);
+    else if (dk == 64) rc = launch<64>(p, n_seqs, max_new_tokens, n_tokens, true, stream);
+    else rc = launch<128>(p, n_seqs, max_new_tokens, n_tokens, true, stream);
+    LLM_REQUIRE(rc == 0, "gated_attention_mma: cannot raise the shared memory limit");
+    LLM_CHECK_LAUNCH("gated_attention_mma");
+    return LLM_OK;
+  }
 #define LLM_GATED(K, V) if (dk == K && dv == V) rc = launch_plain<K, V>(p, n_seqs, max_new_tokens, stream)
   LLM_GATED(32, 32); LLM_GATED(32, 64); LLM_GATED(32, 128);
   LLM_GATED(64, 32); LLM_GATED(64, 64); LLM_GATED(64, 128);

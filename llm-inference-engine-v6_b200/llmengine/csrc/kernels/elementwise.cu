@@ -476,12 +476,39 @@ __global__ void norm_add_kernel(float* __restrict__ h, const float* __restrict__
   float keep[NA_MAX];
   float ss = 0.f;
   if (KEEP) {
+    // part after part for all of the thread's elements at once: NA_MAX loads on their way at a time, and every element still
+    // adds its parts in index order (a before b)
 #pragma unroll
     for (int k = 0; k < NA_MAX; ++k) {
       const int i = threadIdx.x + k * blockDim.x;
-      keep[k] = i < dim ? sum_at(i) : 0.f;
-      ss += keep[k] * keep[k];
+      keep[k] = i < dim ? a[base + i] : 0.f;
     }
+    for (int p = 1; p < na; ++p) {
+#pragma unroll
+      for (int k = 0; k < NA_MAX; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < dim) keep[k] += a[(size_t)p * sa + base + i];
+      }
+    }
+    if (b) {
+      float other[NA_MAX];
+#pragma unroll
+      for (int k = 0; k < NA_MAX; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        other[k] = i < dim ? b[base + i] : 0.f;
+      }
+      for (int p = 1; p < nb; ++p) {
+#pragma unroll
+        for (int k = 0; k < NA_MAX; ++k) {
+          const int i = threadIdx.x + k * blockDim.x;
+          if (i < dim) other[k] += b[(size_t)p * sb + base + i];
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < NA_MAX; ++k) keep[k] += other[k];
+    }
+#pragma unroll
+    for (int k = 0; k < NA_MAX; ++k) ss += keep[k] * keep[k];
   } else {
     for (int i = threadIdx.x; i < dim; i += blockDim.x) {
       const float y = sum_at(i);

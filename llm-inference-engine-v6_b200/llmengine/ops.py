@@ -1116,11 +1116,22 @@ class CudaOps:
         if q.dtype == torch.bfloat16 and self.tensor_cores and self.gated_attention_tensor_cores:
             lib = self.lib("tensorcore")
             if lib.llm_gated_attention_mma_supported(c_int(nq), c_int(nkv), c_int(dk), c_int(dv), c_longlong(q.stride(0)), c_longlong(out.stride(0))):
+                n_splits, split_keys, scratch = 1, 256, None
+                if batch.max_new_tokens == 1 and batch.n_tokens == batch.n_seqs and dk == dv:
+                    # single decoded tokens: the keys a token may see (its chunk at most) in pieces side by side
+                    reach = min(batch.max_seq_len, chunk) if chunk > 0 else batch.max_seq_len
+                    n_splits, split_keys = self._split_policy(batch.n_seqs * nkv, reach, dk)
+                    if n_splits > 1:
+                        floats = int(lib.llm_attention_mma_scratch_floats(c_int(batch.n_tokens), c_int(nq), c_int(dv), c_int(n_splits)))
+                        scratch = batch.ws.get("attention.splits", (floats,), torch.float32)
                 self._check(lib.llm_gated_attention_mma(
                     _ptr(q), c_longlong(q.stride(0)), _ptr(kcache), _ptr(vcache), _ptr(batch.seq_start), _ptr(batch.seq_ntok), _ptr(batch.seq_qoff),
                     _ptr(block_table), c_int(block_table.shape[1]), _ptr(out), c_longlong(out.stride(0)), c_int(batch.n_seqs),
                     c_int(batch.max_new_tokens), c_int(nq), c_int(nkv), c_int(dk), c_int(dv), c_int(page), c_float(scale), c_int(window),
-                    c_int(chunk), _ptr(sink), _ptr(gate), c_int(gp), c_longlong(gs), c_int(gw), c_int(gate_off), _stream()), lib)
+                    c_int(chunk), _ptr(sink), _ptr(gate), c_int(gp), c_longlong(gs), c_int(gw), c_int(gate_off), c_int(batch.n_tokens),
+                    c_int(n_splits), c_int(split_keys), _ptr(scratch), _stream()), lib)
+                if n_splits > 1:
+                    self.launches += 1  # the kernel that merges the pieces
                 return out
         lib = self.lib()
         self._check(lib.llm_gated_attention_simt(_ptr(q), c_longlong(q.stride(0)), _ptr(kcache), _ptr(vcache), c_int(dtype_code(q.dtype)),

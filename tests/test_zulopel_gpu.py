@@ -113,7 +113,7 @@ def mixer_harness(dt, spec, page, part):
 def _one_attention_layer(heads, kv_heads, dim, vdim, chunk, dims):
     """A configuration of one attention layer, for the head sizes that the tensor-core kernel takes."""
     from tiny_zulopel import _att
-    return {"architecture": "Zulopel", "vocab": 64, "width": 80, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0}, "max_positions": 256,
+    return {"architecture": "Zulopel", "vocab": 64, "width": 80, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0}, "max_positions": 2048,
             "layers": [{"type": "attention", "mixer": _att(heads, kv_heads, dim, vdim, dim ** -0.5, dims, 1000.0, chunk), "mlp": None}]}
 
 
@@ -139,6 +139,48 @@ def test_gated_attention_alone(dt, cfg, i, sharp):
         got = whole(part.forward(x[lo:hi].to(DEV), ctx, cache)).cpu()
         ref = P.attention_mixer(x[lo:hi].double(), cpu, f"l{i}.mix.", cfg["layers"][i]["mixer"], cfg["norm"]["eps"], lo, state, {})
         close(got, ref, dt, f"positions {lo}..{hi}")
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("chunk", [0, 700])
+def test_gated_attention_single_tokens_after_a_long_context(dt, chunk):
+    """1,500 tokens as one portion, then single tokens: in bfloat16 their key range runs in pieces side by side (counted from
+    the chunk's start) and the sink and the gate are applied where the pieces are merged. The oracle forms every key and value
+    at once and the last tokens' scores by one product each."""
+    cfg = _one_attention_layer(8, 2, 64, 64, chunk, 32)
+    m, eps = cfg["layers"][0]["mixer"], cfg["norm"]["eps"]
+    cpu, dev, spec = layer_tensors(cfg, 0, dt, sharp=True)
+    h, cache = mixer_harness(dt, spec, 16, build_part("mixer", spec.mixer, Harness(dt).env))
+    part = build_part("mixer", spec.mixer, h.env)
+    part.load(dev)
+    if dt == torch.bfloat16:
+        assert get_ops()._split_policy(2, min(1503, chunk) if chunk else 1503, 64)[0] > 1, "the case is meant to run in pieces"
+    T = 1503
+    x = (2 * torch.randn(T, cfg["width"], generator=torch.Generator().manual_seed(26))).to(dt)
+    w = {k[len("l0.mix."):]: v for k, v in cpu.items() if k.startswith("l0.mix.")}
+    xd = x.double()
+    q = P.rms_norm((xd @ w["q"].T).view(T, 8, 64), w["q.norm"], eps)
+    k = P.rms_norm((xd @ w["k"].T).view(T, 2, 64), w["k.norm"], eps)
+    v = (xd @ w["v"].T).view(T, 2, 64)
+    for t in range(T):
+        q[t], k[t] = P.rotate(q[t], t, m["rot"]), P.rotate(k[t], t, m["rot"])
+    gate = torch.sigmoid(xd @ w["g"].T)
+
+    def oracle(t):
+        lo = (t // chunk) * chunk if chunk else 0
+        heads = []
+        for a in range(8):
+            s = (k[lo:t + 1, a // 4] @ q[t, a]) * m["scale"]
+            p = torch.softmax(torch.cat([s, w["sink"][a:a + 1]]), dim=0)[:-1]
+            heads.append(p @ v[lo:t + 1, a // 4])
+        return (torch.cat(heads) * gate[t]) @ w["o"].T
+
+    got = whole(part.forward(x[:1500].to(DEV), h.ctx([(1, 1500, [])]), cache)).cpu()
+    for t in (0, 63, 699, 700, 1399, 1400, 1499):
+        close(got[t], oracle(t), dt, f"position {t} of the portion")
+    for t in (1500, 1501, 1502):
+        got = whole(part.forward(x[t:t + 1].to(DEV), h.ctx([(1, 1, [])]), cache)).cpu()
+        close(got[0], oracle(t), dt, f"single token at {t}")
 
 
 @pytest.mark.parametrize("dt", DTYPES)
