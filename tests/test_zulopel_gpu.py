@@ -183,8 +183,20 @@ def test_gated_attention_single_tokens_after_a_long_context(dt, chunk):
         close(got[0], oracle(t), dt, f"single token at {t}")
 
 
+def _one_scan_layer(inner, state, conv, dt_rank):
+    from tiny_zulopel import _scan
+    return {"architecture": "Zulopel", "vocab": 64, "width": 80, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0}, "max_positions": 512,
+            "layers": [{"type": "mamba1", "mixer": _scan(inner, state, conv, dt_rank), "mlp": None}]}
+
+
+# (the last two: a rank and a channel count that the tensor-core step-size product takes, with states of 5 and 24 numbers, whose
+# rows of B and C are not 16-byte aligned in the first)
+SCAN_CASES = [(ZULOPEL_A, 0), (ZULOPEL_A, 3), (ZULOPEL_B, 1), (ZULOPEL_B, 2), (ZULOPEL_C, 0), (_one_scan_layer(64, 5, 3, 8), 0),
+              (_one_scan_layer(48, 24, 4, 16), 0)]
+
+
 @pytest.mark.parametrize("dt", DTYPES)
-@pytest.mark.parametrize("cfg,i", [(ZULOPEL_A, 0), (ZULOPEL_A, 3), (ZULOPEL_B, 1), (ZULOPEL_B, 2), (ZULOPEL_C, 0)], ids=["a0", "a3", "b1", "b2", "c0"])
+@pytest.mark.parametrize("cfg,i", SCAN_CASES, ids=["a0", "a3", "b1", "b2", "c0", "n5", "n24"])
 def test_selective_scan_alone(dt, cfg, i):
     """Portions of 1, 2 and many tokens that hand the convolution's inputs and the state on through the slot."""
     cpu, dev, spec = layer_tensors(cfg, i, dt)
