@@ -536,6 +536,75 @@ __global__ void norm_add_kernel(float* __restrict__ h, const float* __restrict__
 }
 }  // namespace
 
+namespace {
+// The same for rows of a multiple of 4 numbers behind 16-byte aligned pointers: a thread has up to two groups of four
+// neighbouring numbers and moves them by 16-byte loads and stores; every number still adds its parts in index order.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+    norm_add_vec_kernel(float* __restrict__ h, const float* __restrict__ a, int na, size_t sa, const float* __restrict__ b, int nb, size_t sb,
+                        const float* __restrict__ w, const float* __restrict__ ls, float eps, T* __restrict__ copy, int dim) {
+  __shared__ float red[33];
+  dep_launch();
+  dep_wait();
+  const size_t base = (size_t)blockIdx.x * dim;
+  const int groups = dim / 4;
+  float4 y[2];
+  bool has[2];
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int g = threadIdx.x + k * blockDim.x;
+    has[k] = g < groups;
+    y[k] = has[k] ? *reinterpret_cast<const float4*>(a + base + 4 * g) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (int p = 1; p < na; ++p) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      if (has[k]) {
+        const float4 v = *reinterpret_cast<const float4*>(a + (size_t)p * sa + base + 4 * (threadIdx.x + k * blockDim.x));
+        y[k].x += v.x; y[k].y += v.y; y[k].z += v.z; y[k].w += v.w;
+      }
+    }
+  }
+  if (b) {
+    float4 o[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k)
+      o[k] = has[k] ? *reinterpret_cast<const float4*>(b + base + 4 * (threadIdx.x + k * blockDim.x)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p = 1; p < nb; ++p) {
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        if (has[k]) {
+          const float4 v = *reinterpret_cast<const float4*>(b + (size_t)p * sb + base + 4 * (threadIdx.x + k * blockDim.x));
+          o[k].x += v.x; o[k].y += v.y; o[k].z += v.z; o[k].w += v.w;
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) { y[k].x += o[k].x; y[k].y += o[k].y; y[k].z += o[k].z; y[k].w += o[k].w; }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < 2; ++k) ss += y[k].x * y[k].x + y[k].y * y[k].y + y[k].z * y[k].z + y[k].w * y[k].w;
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    if (!has[k]) continue;
+    const int i = 4 * (threadIdx.x + k * blockDim.x);
+    const float4 wv = *reinterpret_cast<const float4*>(w + i);
+    float4 v = make_float4(y[k].x * inv * wv.x, y[k].y * inv * wv.y, y[k].z * inv * wv.z, y[k].w * inv * wv.w);
+    if (ls) {
+      const float4 l = *reinterpret_cast<const float4*>(ls + i);
+      v.x *= l.x; v.y *= l.y; v.z *= l.z; v.w *= l.w;
+    }
+    float4 x = *reinterpret_cast<const float4*>(h + base + i);
+    x.x += v.x; x.y += v.y; x.z += v.z; x.w += v.w;
+    *reinterpret_cast<float4*>(h + base + i) = x;
+    if (copy) store4<T>(copy + base + i, x.x, x.y, x.z, x.w);
+  }
+}
+}  // namespace
+
 extern "C" int llm_norm_add(float* h, const float* a, int na, long long sa, const float* b, int nb, long long sb, const float* w,
                             const float* ls, float eps, void* copy, int copy_dtype, int n_rows, int dim, cudaStream_t stream) {
   if (n_rows == 0) return LLM_OK;
@@ -544,6 +613,17 @@ extern "C" int llm_norm_add(float* h, const float* a, int na, long long sa, cons
   LLM_REQUIRE(copy_dtype == LLM_F32 || copy_dtype == LLM_BF16, "norm_add: unknown dtype %d", copy_dtype);
 #define LLM_NA(T, KEEP) \
   launch_kernel(norm_add_kernel<T, KEEP>, n_rows, threads, 0, stream, h, a, na, (size_t)sa, b, nb, (size_t)sb, w, ls, eps, (T*)copy, dim)
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (dim % 4 == 0 && dim / 4 <= 2048 && al16(h) && al16(a) && al16(b) && al16(w) && al16(ls) && al16(copy) && sa % 4 == 0 && sb % 4 == 0) {
+    int vt = ((dim / 4 + 1) / 2 + 31) / 32 * 32;  // two groups of four a thread
+    vt = vt < 64 ? 64 : vt;
+    if (copy_dtype == LLM_F32)
+      launch_kernel(norm_add_vec_kernel<float>, n_rows, vt, 0, stream, h, a, na, (size_t)sa, b, nb, (size_t)sb, w, ls, eps, (float*)copy, dim);
+    else
+      launch_kernel(norm_add_vec_kernel<bf16>, n_rows, vt, 0, stream, h, a, na, (size_t)sa, b, nb, (size_t)sb, w, ls, eps, (bf16*)copy, dim);
+    LLM_CHECK_LAUNCH("norm_add");
+    return LLM_OK;
+  }
   const bool keep = dim <= NA_MAX * threads;
   if (copy_dtype == LLM_F32) { if (keep) LLM_NA(float, true); else LLM_NA(float, false); }
   else { if (keep) LLM_NA(bf16, true); else LLM_NA(bf16, false); }

@@ -213,15 +213,20 @@ def test_selective_scan_alone(dt, cfg, i):
         close(got, ref, dt, f"positions {lo}..{hi}")
 
 
-def test_norm_on_the_output_with_layer_scale_alone():
+@pytest.mark.parametrize("dim,rows", [(50, 7), (72, 5), (2048, 3), (4100, 2), (9000, 2)])
+def test_norm_on_the_output_with_layer_scale_alone(dim, rows):
+    """Rows of any length (the kernel has a form with 16-byte moves, one that keeps a row in registers and one that reads it twice)."""
     g = torch.Generator().manual_seed(3)
-    hstream, a, b = torch.randn(7, 50, generator=g), torch.randn(3, 7, 50, generator=g), torch.randn(7, 50, generator=g)
-    w, ls = 1 + 0.3 * torch.randn(50, generator=g), 1 + 0.3 * torch.randn(50, generator=g)
+    hstream, a, b = torch.randn(rows, dim, generator=g), torch.randn(3, rows, dim, generator=g), torch.randn(rows, dim, generator=g)
+    w, ls = 1 + 0.3 * torch.randn(dim, generator=g), 1 + 0.3 * torch.randn(dim, generator=g)
     want = hstream.double() + P.rms_norm(a.double().sum(0) + b.double(), w.double(), 1e-3) * ls.double()
-    hd, copy = hstream.to(DEV), torch.empty(7, 50, dtype=torch.bfloat16, device=DEV)
+    hd, copy = hstream.to(DEV), torch.empty(rows, dim, dtype=torch.bfloat16, device=DEV)
     get_ops().norm_add(hd, a.to(DEV), b.to(DEV), w.to(DEV), ls.to(DEV), 1e-3, copy=copy)
     np.testing.assert_allclose(hd.cpu().numpy(), want.numpy(), rtol=0, atol=2e-5)
     assert torch.equal(copy.cpu(), hd.cpu().to(torch.bfloat16))
+    h2 = hstream.to(DEV)  # one set of sums, no layer scale, no copy
+    get_ops().norm_add(h2, b.to(DEV), None, w.to(DEV), None, 1e-3)
+    np.testing.assert_allclose(h2.cpu().numpy(), (hstream.double() + P.rms_norm(b.double(), w.double(), 1e-3)).numpy(), rtol=0, atol=2e-5)
 
 
 # ---------------------------------------------------------------------------------------------- whole models
