@@ -186,13 +186,13 @@ class PostNormBlock(Block):
             res.pending = None
         res.sumsq = res.prescaled = res.prescaled_weight = None
         a = self.mixer.forward(xs, ctx, cache)
-        ops.norm_add(res.h, a, None, self.norm1.weight, self.scale1, self.norm1.spec.eps, copy=None if same else xs, n_rows=n)
+        ops.norm_add(res.h, a, None, self.norm1.prescale_weight(), self.scale1, self.norm1.spec.eps, copy=None if same else xs, n_rows=n)
         if self.feed_forward is not None:
             ctx.takes_delta_pairs = True  # a feed-forward made of two branches may hand both sets of sums over: one kernel adds them
             b = self.feed_forward.forward(xs, ctx)
             ctx.takes_delta_pairs = False
             b, b2 = b if isinstance(b, tuple) else (b, None)
-            ops.norm_add(res.h, b, b2, self.norm2.weight, self.scale2, self.norm2.spec.eps, copy=None if same else xs, n_rows=n)
+            ops.norm_add(res.h, b, b2, self.norm2.prescale_weight(), self.scale2, self.norm2.spec.eps, copy=None if same else xs, n_rows=n)
         res.operand = None if same else xs  # valid until somebody else writes the stream
         return res
 
